@@ -24,7 +24,9 @@ table[p // page] * page + p % page, `ensure` that raises before it allocates any
 
 Device storage of a paged group: [entries, pages of the group + 1, 2, kv_heads, page_size, head_dim] (the last
 page is the group's padding page, never handed out)
-(K plane then V plane of a page; one head's rows of a page are contiguous).
+(K plane then V plane of a page; one head's rows of a page are contiguous).  A group whose need names a
+`value_dim` keeps [entries, pages + 1, kv_heads * page_size * (head_dim + value_dim)]: the same two planes, of
+different widths, as one flat row per page.
 """
 from __future__ import annotations
 
@@ -165,8 +167,12 @@ class CacheManager:
                 # one page more than the pool hands out: the group's padding page.  Rows that only pad a batch to a
                 # size with a captured graph read and write there (the reference keeps such a scratch page too,
                 # engine/engine.py:207-211)
-                g.storage = torch.zeros((len(g.entries), g.pool.num_pages + 1, 2, n.kv_heads, self.page_size, n.head_dim),
-                                        dtype=self.dtype, device=self.device)
+                if n.value_dim:
+                    # values of another width than keys: a page is one flat row, key plane then value plane
+                    shape = (len(g.entries), g.pool.num_pages + 1, n.page_elements(self.page_size))
+                else:
+                    shape = (len(g.entries), g.pool.num_pages + 1, 2, n.kv_heads, self.page_size, n.head_dim)
+                g.storage = torch.zeros(shape, dtype=self.dtype, device=self.device)
             else:
                 dt = getattr(torch, g.need.state_dtype)
                 g.storage = torch.zeros((len(g.entries), self.max_requests + 1) + tuple(g.need.state_shape),
@@ -192,7 +198,7 @@ class CacheManager:
     def bytes_for(needs: list, page_size: int, num_pages: int, itemsize: int, max_requests: int,
                   max_step_tokens: int | None) -> int:
         """Bytes of the paged storage with `num_pages` pages: every cache entry pays for the pages of its group's pool."""
-        return sum(2 * n.kv_heads * n.head_dim * page_size * itemsize
+        return sum(n.page_elements(page_size) * itemsize
                    * (CacheManager.pool_pages(n, page_size, num_pages, max_requests, max_step_tokens) + 1)
                    for n in needs if n.kind == "paged_kv")
 
@@ -213,8 +219,8 @@ class CacheManager:
         return lo
 
     def view(self, entry: int):
-        """(group index, storage of that cache entry): [pages, 2, kv_heads, page, head_dim] or
-        [max_requests, *state_shape]."""
+        """(group index, storage of that cache entry): [pages, 2, kv_heads, page, head_dim] (with a `value_dim`:
+        [pages, numbers of a page], key plane then value plane) or [max_requests, *state_shape]."""
         cached = self._views.get(entry)
         if cached is not None:
             return cached

@@ -12,6 +12,7 @@ import os
 from .errors import ConfigError
 
 ARCHITECTURES: dict = {}
+_builtin_loaded = False
 
 
 def register_architecture(arch) -> None:
@@ -22,8 +23,10 @@ def register_architecture(arch) -> None:
 def architecture_for(config_dict: dict):
     _ensure_builtin()
     names = config_dict.get("architectures") or []
+    if not names and isinstance(config_dict.get("architecture"), str):
+        names = [config_dict["architecture"]]          # some families name themselves with one string
     if not names:
-        raise ConfigError("config.json lacks 'architectures'; known: " + ", ".join(sorted(ARCHITECTURES)))
+        raise ConfigError("config.json lacks 'architectures' (or 'architecture'); known: " + ", ".join(sorted(ARCHITECTURES)))
     name = names[0]
     if name not in ARCHITECTURES:
         raise ConfigError(f"architecture {name!r} is not registered; known: "
@@ -43,5 +46,7 @@ def load_config(model_dir: str):
 
 
 def _ensure_builtin() -> None:
-    if not ARCHITECTURES:
-        from ..models import llama  # noqa: F401  (registers itself)
+    global _builtin_loaded
+    if not _builtin_loaded:
+        _builtin_loaded = True
+        from ..models import lifusun, llama  # noqa: F401  (they register themselves)

@@ -41,6 +41,9 @@ class CacheNeed:
 
     kind "paged_kv": `kv_heads * head_dim` keys and as many values per token, in pages.
         window == 0 keeps every token, window > 0 only the last `window` tokens.
+        value_dim == 0: values are as wide as keys and a page is [2, kv_heads, page, head_dim];
+        value_dim > 0: a value head has `value_dim` numbers and a page is one flat row, the
+        key plane [kv_heads, page, head_dim] followed by the value plane [kv_heads, page, value_dim].
     kind "state":    a fixed-size record per request (`state_shape`, `state_dtype`).
     kind "none":     nothing.
     Layers whose needs compare equal share one group of the cache manager.
@@ -51,6 +54,11 @@ class CacheNeed:
     window: int = 0
     state_shape: tuple = ()
     state_dtype: str = "float32"
+    value_dim: int = 0
+
+    def page_elements(self, page_size: int) -> int:
+        """Numbers one page of one cache entry holds."""
+        return self.kv_heads * page_size * (self.head_dim + (self.value_dim or self.head_dim))
 
 
 @dataclass(frozen=True)
@@ -60,6 +68,7 @@ class MixerSpec:
     heads: int = 0
     kv_heads: int = 0
     head_dim: int = 0
+    value_dim: int = 0           # 0 = head_dim
     window: int = 0              # 0 = all earlier tokens
     softmax_scale: float = 0.0   # 0 = 1/sqrt(head_dim)
     position: PositionSpec | None = None
@@ -133,10 +142,14 @@ class LayerCall:
     cache:  index of the cache entry the mixer reads; normally the call's own index
             in the run order, another call's index to read that call's cache.
     write:  whether this call stores its new keys/values/state in that entry.
+    state:  index of a second cache entry, of kind "state", that the call's mixer keeps beside the first
+            (what a short convolution remembers of a request's last tokens, say); None if it keeps none.
+            The mixer's class names its shape with `state_need(spec)`.
     """
     layer: int
     cache: int
     write: bool = True
+    state: int | None = None
 
 
 @dataclass(frozen=True)
@@ -162,4 +175,4 @@ class ModelSpec:
 
     def cache_entries(self) -> int:
         """Number of distinct cache entries the run order writes."""
-        return len({c.cache for c in self.order if c.write})
+        return len({c.cache for c in self.order if c.write} | {c.state for c in self.order if c.state is not None})

@@ -1,0 +1,208 @@
+// Paged attention whose heads talk to each other before the softmax, general form (float32 arithmetic, any
+// sizes): for a query at position i of a request and every key j it sees,
+//     s[g, j] = scale * q[g] . k[kv(g), j] - slope[g] * (i - j)          all query heads g
+//     a[h, j] = sum_g talk[h, g] * s[g, j]
+//     p[h, :] = softmax_j a[h, :],     out[h] = sum_j p[h, j] v[kv(h), j]
+// A query sees the keys j <= i of its request; with chunk > 0 only those of its own chunk (j / chunk == i / chunk,
+// counted from the request's position 0).  Because every head's score of a key enters every head's softmax,
+// one block works on all heads of a token: the scores of a tile of 32 keys land in shared memory, are mixed there,
+// and then each warp runs the running softmax and the value sum of its heads.
+//
+// Key tiles start at multiples of 32 of the key position and sums run in a fixed order, so a position's result
+// does not depend on how the request was cut into steps or on what else is in the batch.
+//
+// Cache layout: pages of `page_stride` elements; key plane [kv_heads, page_size, dim], then, `v_off` elements in,
+// value plane [kv_heads, page_size, vdim].
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTile = 32;
+constexpr int kMaxValueDim = 256;
+
+template <typename T>
+__device__ __forceinline__ float dot_any(const T* __restrict__ k, const float* __restrict__ q, int d, bool vec);
+
+template <>
+__device__ __forceinline__ float dot_any<float>(const float* __restrict__ k, const float* __restrict__ q, int d, bool vec) {
+    float acc = 0.f;
+    if (vec) {
+        for (int i = 0; i < d; i += 4) {
+            const float4 kv = *reinterpret_cast<const float4*>(k + i);
+            acc = fmaf(kv.x, q[i], acc);
+            acc = fmaf(kv.y, q[i + 1], acc);
+            acc = fmaf(kv.z, q[i + 2], acc);
+            acc = fmaf(kv.w, q[i + 3], acc);
+        }
+    } else {
+        for (int i = 0; i < d; ++i) acc = fmaf(k[i], q[i], acc);
+    }
+    return acc;
+}
+
+template <>
+__device__ __forceinline__ float dot_any<__nv_bfloat16>(const __nv_bfloat16* __restrict__ k, const float* __restrict__ q,
+                                                         int d, bool vec) {
+    float acc = 0.f;
+    if (vec) {
+        for (int i = 0; i < d; i += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(p[j]);
+                acc = fmaf(f.x, q[i + 2 * j], acc);
+                acc = fmaf(f.y, q[i + 2 * j + 1], acc);
+            }
+        }
+    } else {
+        for (int i = 0; i < d; ++i) acc = fmaf(__bfloat162float(k[i]), q[i], acc);
+    }
+    return acc;
+}
+
+template <typename T, int HPW>
+__global__ void talking_attn_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache, long long page_stride,
+                                    long long v_off, const int* __restrict__ block_table, int table_width,
+                                    const int* __restrict__ token_request, const int* __restrict__ positions,
+                                    const float* __restrict__ talk, const float* __restrict__ slopes,
+                                    T* __restrict__ out, int out_stride, int heads, int kv_heads, int dim, int vdim,
+                                    int page_size, int chunk, float scale, int vec) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float smem[];
+    float* qs = smem;                           // [heads, dim]
+    float* talk_s = qs + heads * dim;           // [heads, heads]
+    float* S = talk_s + heads * heads;          // [heads, kTile] scores before mixing
+    float* A = S + heads * kTile;               // [heads, kTile] after mixing
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[t];
+    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const int* table = block_table + (size_t)token_request[t] * table_width;
+    const int group = heads / kv_heads;
+
+    for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) qs[i] = to_f32(q[(size_t)t * q_stride + i]);
+    for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) talk_s[i] = talk[i];
+
+    constexpr int kOwn = kMaxValueDim / 32;
+    float acc[HPW][kOwn], m[HPW], l[HPW];
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kOwn; ++r) acc[i][r] = 0.f;
+    }
+    __syncthreads();
+
+    for (int k0 = lo & ~(kTile - 1); k0 <= pos; k0 += kTile) {
+        const int j = k0 + lane;
+        const bool valid = j >= lo && j <= pos;
+        long long page_base = 0;
+        int off = 0;
+        if (valid) {
+            page_base = (long long)table[j / page_size] * page_stride;
+            off = j % page_size;
+        }
+        // scores of all heads for the tile's keys: a warp takes one head at a time, a lane one key
+        for (int g = warp; g < heads; g += (blockDim.x >> 5)) {
+            float s = 0.f;
+            if (valid) {
+                const T* krow = cache + page_base + ((size_t)(g / group) * page_size + off) * dim;
+                s = scale * dot_any<T>(krow, qs + g * dim, dim, vec != 0) - slopes[g] * (float)(pos - j);
+            }
+            S[g * kTile + lane] = s;
+        }
+        __syncthreads();
+        for (int h = warp; h < heads; h += (blockDim.x >> 5)) {
+            float a = 0.f;
+            for (int g = 0; g < heads; ++g) a = fmaf(talk_s[h * heads + g], S[g * kTile + lane], a);
+            A[h * kTile + lane] = valid ? a : -INFINITY;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < HPW; ++i) {
+            const int h = warp * HPW + i;
+            if (h >= heads) break;                       // the whole warp leaves together
+            const float s = A[h * kTile + lane];
+            const float m_new = fmaxf(m[i], warp_max(s));   // finite: every tile holds a visible key
+            const float corr = expf(m[i] - m_new);          // 0 on the first tile
+            const float p = valid ? expf(s - m_new) : 0.f;
+            l[i] = l[i] * corr + warp_sum(p);
+            m[i] = m_new;
+#pragma unroll
+            for (int r = 0; r < kOwn; ++r) acc[i][r] *= corr;
+            const long long vo = page_base + v_off + ((long long)(h / group) * page_size + off) * vdim;
+            for (int jj = 0; jj < kTile; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const long long vrow = __shfl_sync(0xffffffffu, vo, jj);
+                if (pj == 0.f) continue;                 // same for the whole warp
+                const T* v = cache + vrow;
+#pragma unroll
+                for (int r = 0; r < kOwn; ++r) {
+                    const int d = lane + 32 * r;
+                    if (d < vdim) acc[i][r] = fmaf(pj, to_f32(v[d]), acc[i][r]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int h = warp * HPW + i;
+        if (h >= heads) break;
+        const float inv = 1.0f / l[i];
+        T* orow = out + (size_t)t * out_stride + (size_t)h * vdim;
+#pragma unroll
+        for (int r = 0; r < kOwn; ++r) {
+            const int d = lane + 32 * r;
+            if (d < vdim) orow[d] = from_f32<T>(acc[i][r] * inv);
+        }
+    }
+}
+
+template <typename T, int HPW>
+int launch_talking(const void* q, int q_stride, const void* cache, long long page_stride, long long v_off,
+                   const int* block_table, int table_width, const int* token_request, const int* positions,
+                   const float* talk, const float* slopes, void* out, int out_stride, int tokens, int heads, int kv_heads,
+                   int dim, int vdim, int page_size, int chunk, float scale, int vec, cudaStream_t stream) {
+    const int warps = (heads + HPW - 1) / HPW;
+    const size_t smem = sizeof(float) * ((size_t)heads * dim + (size_t)heads * heads + 2 * (size_t)heads * kTile);
+    if (smem > 200 * 1024) LLM_FAIL(-1, "talking attention: %d heads of %d dims do not fit shared memory", heads, dim);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(talking_attn_kernel<T, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    llm_launch(talking_attn_kernel<T, HPW>, tokens, warps * 32, smem, stream, (const T*)q, q_stride, (const T*)cache,
+               page_stride, v_off, block_table, table_width, token_request, positions, talk, slopes, (T*)out, out_stride,
+               heads, kv_heads, dim, vdim, page_size, chunk, scale, vec);
+    LLM_CHECK_LAUNCH("talking_attention");
+    return 0;
+}
+
+}  // namespace
+
+LLM_API int llm_talking_attention(const void* q, int q_stride, const void* cache, long long page_stride, long long v_off,
+                                  const int* block_table, int table_width, const int* token_request,
+                                  const int* positions, const float* talk, const float* slopes, void* out,
+                                  int out_stride, int dtype, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                  int page_size, int chunk, float scale, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (vdim <= 0 || vdim > kMaxValueDim) LLM_FAIL(-1, "talking attention: value size %d is not in [1, %d]", vdim, kMaxValueDim);
+    if (kv_heads <= 0 || heads % kv_heads) LLM_FAIL(-1, "talking attention: heads %d is not a multiple of kv_heads %d", heads, kv_heads);
+    if (heads > 64) LLM_FAIL(-1, "talking attention: %d heads (at most 64)", heads);
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        const int per16 = 16 / (int)sizeof(T);        // elements of a 16-byte load
+        const int vec = (dim % per16 == 0 && vdim % per16 == 0 && page_stride % per16 == 0) ? 1 : 0;
+#define LLM_TALK(HPW)                                                                                                   \
+    launch_talking<T, HPW>(q, q_stride, cache, page_stride, v_off, block_table, table_width, token_request, positions,  \
+                           talk, slopes, out, out_stride, tokens, heads, kv_heads, dim, vdim, page_size, chunk, scale,  \
+                           vec, stream)
+        if (heads <= 16) return LLM_TALK(1);
+        if (heads <= 32) return LLM_TALK(2);
+        return LLM_TALK(4);
+#undef LLM_TALK
+    });
+}
+
+LLM_TRACE_EXPORT(talking_attention)

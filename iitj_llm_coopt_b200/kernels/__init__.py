@@ -86,6 +86,16 @@ _SIGNATURES = {
     "llm_sample_scratch_floats": [_c_int, _c_int],
     "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "llm_attention_decode_status": [],
+    "llm_conv_norm_store": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                            _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int,
+                            _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_talking_attention": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
+                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                              _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_retention_scan": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+    "llm_retention_headnorm_gate": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                    _c_void_p],
 }
 
 # The library's health words in the order llm_sample copies them out (csrc/common.cuh): which kernel, and what its codes mean.
@@ -598,6 +608,127 @@ class Kernels:
                        heads, kv_heads, head_dim, cache_layer.shape[3], int(window), float(scale), kps, splits, self._stream())
         if splits > 1:
             self.launches += 1      # the merge kernel
+        return out
+
+
+    # ---- mixers with state: short convolution, talking-heads attention, retention ------------------------
+    @staticmethod
+    def _page_size_of(cache_layer, kv_heads, head_dim, value_dim) -> int:
+        per_token = kv_heads * (head_dim + value_dim)
+        _need(cache_layer.dim() == 2 and cache_layer.shape[1] % per_token == 0,
+              f"cache: a page of {tuple(cache_layer.shape)} is not key plane + value plane of {kv_heads} heads of {head_dim} + {value_dim}")
+        return cache_layer.shape[1] // per_token
+
+    def conv_norm_store(self, u, bias, taps_w, q_gain, k_gain, state, state_slots, token_request, cu_seqlens, q_out,
+                        cache_layer, slots, heads, kv_heads, head_dim, value_dim, eps):
+        """Bias, short causal convolution over time, norms, and the store of keys and values (csrc/short_conv.cu).
+
+        u [T, C] is the fused projection: query channels, then (when `cache_layer` is given) key and value channels.
+        bias [C], taps_w [C, taps], q_gain, k_gain: float32 (bias / taps_w None: no bias / one tap).  state
+        [slots, taps - 1, C] float32 holds every request's last projected rows and is brought up to date.  Writes the
+        normed queries to q_out [T, heads * head_dim] and, at `slots`, normed keys and values into cache_layer
+        [pages, kv_heads * page * (head_dim + value_dim)]."""
+        _check(u, "conv_norm_store.u", tuple(DTYPE_CODE), 2)
+        tokens, channels = u.shape
+        own = cache_layer is not None
+        _need(channels == heads * head_dim + (kv_heads * (head_dim + value_dim) if own else 0), "conv_norm_store.u: wrong width")
+        taps = 1
+        if taps_w is not None:
+            _check(taps_w, "conv_norm_store.taps", torch.float32, 2)
+            _need(taps_w.shape[0] == channels, "conv_norm_store.taps: one row per channel")
+            taps = taps_w.shape[1]
+        if bias is not None:
+            _check(bias, "conv_norm_store.bias", torch.float32, 1)
+            _need(bias.shape[0] == channels, "conv_norm_store.bias: one per channel")
+        _check(q_gain, "conv_norm_store.q_gain", torch.float32, 1)
+        _need(q_gain.shape[0] == heads * head_dim, "conv_norm_store.q_gain: one per query channel")
+        _check(q_out, "conv_norm_store.q_out", u.dtype, 2)
+        _need(q_out.shape == (tokens, heads * head_dim), "conv_norm_store.q_out: wrong shape")
+        for name, t in (("state_slots", state_slots), ("token_request", token_request), ("cu_seqlens", cu_seqlens)):
+            _check(t, "conv_norm_store." + name, torch.int32, 1)
+        requests = state_slots.shape[0]
+        _need(token_request.shape[0] == tokens and cu_seqlens.shape[0] == requests + 1, "conv_norm_store: index arrays do not fit")
+        if taps > 1:
+            _check(state, "conv_norm_store.state", torch.float32, 3)
+            _need(tuple(state.shape[1:]) == (taps - 1, channels), "conv_norm_store.state: [slots, taps - 1, channels]")
+        page_size, page_stride = 1, 0
+        if own:
+            _check(cache_layer, "conv_norm_store.cache", u.dtype, 2)
+            _check(k_gain, "conv_norm_store.k_gain", torch.float32, 1)
+            _need(k_gain.shape[0] == kv_heads * head_dim, "conv_norm_store.k_gain: one per key channel")
+            _check(slots, "conv_norm_store.slots", torch.int32, 1)
+            _need(slots.shape[0] == tokens, "conv_norm_store.slots: one per token")
+            page_size, page_stride = self._page_size_of(cache_layer, kv_heads, head_dim, value_dim), cache_layer.shape[1]
+        self._call("llm_conv_norm_store", _ptr(u), _ptr(bias), _ptr(taps_w), taps, _ptr(q_gain), _ptr(k_gain) if own else None,
+                   _ptr(state) if taps > 1 else None, _ptr(state_slots), _ptr(token_request), _ptr(cu_seqlens), _ptr(q_out),
+                   _ptr(cache_layer) if own else None, _ptr(slots) if own else None, page_stride, page_size,
+                   DTYPE_CODE[u.dtype], tokens, requests, heads, kv_heads, head_dim, value_dim, float(eps), self._stream())
+        if taps > 1:
+            self.launches += 1      # the state's own kernel
+        return q_out
+
+    def talking_attention(self, q, cache_layer, meta, talk, slopes, out, heads, kv_heads, head_dim, value_dim, chunk, scale):
+        """Attention with a distance bias (slopes [heads]) and heads mixed before the softmax (talk [heads, heads]),
+        over the keys of the query's own chunk (`chunk` 0: all earlier keys); csrc/talking_attention.cu."""
+        _check(q, "talking_attention.q", tuple(DTYPE_CODE), 2)
+        _check(cache_layer, "talking_attention.cache", q.dtype, 2)
+        _check(out, "talking_attention.out", q.dtype, 2)
+        _check(talk, "talking_attention.talk", torch.float32, 2)
+        _check(slopes, "talking_attention.slopes", torch.float32, 1)
+        tokens = q.shape[0]
+        _need(q.shape[1] == heads * head_dim and out.shape == (tokens, heads * value_dim), "talking_attention: q / out shapes do not fit")
+        _need(tuple(talk.shape) == (heads, heads) and slopes.shape[0] == heads, "talking_attention: talk [heads, heads], slopes [heads]")
+        _check(meta.block_table, "talking_attention.block_table", torch.int32, 2)
+        _check(meta.token_request, "talking_attention.token_request", torch.int32, 1)
+        _check(meta.positions, "talking_attention.positions", torch.int32, 1)
+        _need(meta.token_request.shape[0] == tokens and meta.positions.shape[0] == tokens,
+              "talking_attention: one token_request and one position per token")
+        page_size = self._page_size_of(cache_layer, kv_heads, head_dim, value_dim)
+        self._call("llm_talking_attention", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1],
+                   kv_heads * page_size * head_dim, _ptr(meta.block_table), meta.block_table.shape[1], _ptr(meta.token_request),
+                   _ptr(meta.positions), _ptr(talk), _ptr(slopes), _ptr(out), out.shape[1], DTYPE_CODE[q.dtype], tokens,
+                   heads, kv_heads, head_dim, value_dim, page_size, int(chunk), float(scale), self._stream())
+        return out
+
+    def retention(self, proj, tables, rotary_dim, decay, state, state_slots, cu_seqlens, o, heads, head_dim, value_dim,
+                  k_scale, write: bool = True):
+        """The retention scan (csrc/retention.cu): proj [T, >= 2*heads*head_dim + heads*value_dim] holds q, k, v of all
+        heads; tables = (cos, sin) [T, rotary_dim / 2] float32 or None; decay [heads] float32; state
+        [slots, heads, head_dim, value_dim] float32 is read and, with `write`, left at the step's last token;
+        o [T, heads * value_dim] float32."""
+        _check(proj, "retention.proj", tuple(DTYPE_CODE), 2)
+        tokens = proj.shape[0]
+        _need(proj.shape[1] >= 2 * heads * head_dim + heads * value_dim, "retention.proj: row too narrow")
+        _check(decay, "retention.decay", torch.float32, 1)
+        _check(state, "retention.state", torch.float32, 4)
+        _need(decay.shape[0] == heads and tuple(state.shape[1:]) == (heads, head_dim, value_dim), "retention: decay / state shapes do not fit")
+        _check(state_slots, "retention.state_slots", torch.int32, 1)
+        _check(cu_seqlens, "retention.cu_seqlens", torch.int32, 1)
+        _need(cu_seqlens.shape[0] == state_slots.shape[0] + 1, "retention.cu_seqlens: requests + 1 entries")
+        _check(o, "retention.o", torch.float32, 2)
+        _need(o.shape == (tokens, heads * value_dim), "retention.o: wrong shape")
+        cos = sin = None
+        half = rotary_dim // 2
+        if half:
+            cos, sin = tables
+            _check(cos, "retention.cos", torch.float32, 2)
+            _check(sin, "retention.sin", torch.float32, 2)
+            _need(cos.shape == (tokens, half) and sin.shape == cos.shape, "retention: tables must be [tokens, rotary_dim / 2]")
+        self._call("llm_retention_scan", _ptr(proj), proj.shape[1], _ptr(cos), _ptr(sin), half, _ptr(decay), _ptr(state),
+                   _ptr(state_slots), _ptr(cu_seqlens), _ptr(o), DTYPE_CODE[proj.dtype], tokens, state_slots.shape[0], heads,
+                   head_dim, value_dim, float(k_scale), 1 if write else 0, self._stream())
+        return o
+
+    def headnorm_gate(self, o, proj, gate_col, out, heads, value_dim, eps):
+        """out = (each head of o divided by its root mean square) * silu(proj[:, gate_col : gate_col + heads * value_dim])."""
+        _check(o, "headnorm_gate.o", torch.float32, 2)
+        _check(proj, "headnorm_gate.proj", tuple(DTYPE_CODE), 2)
+        _check(out, "headnorm_gate.out", proj.dtype, 2)
+        tokens = o.shape[0]
+        _need(o.shape == (tokens, heads * value_dim) and out.shape == o.shape and proj.shape[0] == tokens and
+              gate_col + heads * value_dim <= proj.shape[1], "headnorm_gate: shapes do not fit")
+        self._call("llm_retention_headnorm_gate", _ptr(o), proj.data_ptr() + gate_col * proj.element_size(), proj.shape[1],
+                   _ptr(out), DTYPE_CODE[proj.dtype], tokens, heads, value_dim, float(eps), self._stream())
         return out
 
     # ---- matrix products -------------------------------------------------------------

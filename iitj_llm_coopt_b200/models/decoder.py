@@ -67,6 +67,10 @@ def cache_needs(spec) -> list:
         for _name, family, part_spec, cls in layer_parts(spec.layers[call.layer]):
             if family == "mixer":
                 need = cls.cache_need(part_spec)
+                if call.state is not None:
+                    if call.state in entries:
+                        raise ValueError(f"cache entry {call.state} is the state of one call and is claimed by another")
+                    entries[call.state] = cls.state_need(part_spec)
         if call.write:
             if call.cache in entries and entries[call.cache] != need:
                 raise ValueError(f"cache entry {call.cache} is written by layers with different needs")

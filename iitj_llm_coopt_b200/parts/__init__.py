@@ -8,18 +8,20 @@ family an arrangement declares for each of its part names and by the `kind` of t
 from __future__ import annotations
 
 from .base import ParamSpec, Part, StepPlan, StepShape
-from .block import Arrangement, PreNormBlock
+from .block import Arrangement, PreNormBlock, PreNormMixerBlock
 from .embedding import Embedding, OutputHead
 from .feed_forward import SwiGLU
 from .mixer import PagedAttention
-from .norm import RMSNorm
+from .retention import Retention
+from .talking_attention import TalkingAttention
+from .norm import RMSNorm, ScalarGainRMSNorm
 from .position import NoPosition, RotaryEmbedding, rope_inverse_frequencies
 
-NORMS = {"rmsnorm": RMSNorm}
+NORMS = {"rmsnorm": RMSNorm, "rmsnorm_scalar": ScalarGainRMSNorm}
 POSITION_ENCODINGS = {"rope": RotaryEmbedding, "none": NoPosition}
-MIXERS = {"attention": PagedAttention}
+MIXERS = {"attention": PagedAttention, "talking_attention": TalkingAttention, "retention": Retention}
 FEED_FORWARDS = {"swiglu": SwiGLU}
-ARRANGEMENTS = {"prenorm": PreNormBlock}
+ARRANGEMENTS = {"prenorm": PreNormBlock, "prenorm_mixer": PreNormMixerBlock}
 EMBEDDINGS = {"table": Embedding}
 HEADS = {"linear": OutputHead}
 

@@ -55,3 +55,12 @@ class PreNormBlock(Arrangement):
         a = self.mixer.forward(ctx, x, call)
         x = self.feed_forward_norm.forward(ctx, residual, delta_for(self.feed_forward_norm, a))
         return residual, self.feed_forward.forward(ctx, x)
+
+
+class PreNormMixerBlock(Arrangement):
+    """A layer without a feed-forward:  x = mixer_norm(residual += delta_in);  delta_out = mixer(x)."""
+    PARTS = {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def forward(self, ctx, residual, delta, call):
+        x = self.mixer_norm.forward(ctx, residual, delta_for(self.mixer_norm, delta))
+        return residual, self.mixer.forward(ctx, x, call)

@@ -26,3 +26,16 @@ class RMSNorm(Part):
         n = rows.shape[0] if rows is not None else residual.shape[0]
         out = ctx.buffer(f"norm.{self.part_name}.out" if rows is None else f"norm.{self.part_name}.rows", (n, self.width), self.dtype)
         return self.k.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows=rows)
+
+
+class ScalarGainRMSNorm(RMSNorm):
+    """RMSNorm whose gain is one number for the whole width: y = x * rsqrt(mean(x^2) + eps) * g.  The
+    checkpoint holds g as a tensor without dimensions; it is spread over the width once, at loading, so the
+    kernel of `RMSNorm` serves both."""
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        return {"weight": ParamSpec((), kind="vector")}
+
+    def load(self, tensors: dict) -> None:
+        self.weight = tensors["weight"].float().reshape(1).expand(self.width).contiguous()

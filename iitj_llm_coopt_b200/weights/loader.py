@@ -108,7 +108,10 @@ def load_parameters(model_dir: str, arch, config, spec, engine_dtype: torch.dtyp
                 file = index[name][0]
                 if file not in handles:
                     handles[file] = safe_open(file, framework="pt", device="cpu")
-                full[row:row + shape[0]].copy_(handles[file].get_tensor(name))
+                if not shape:                         # a tensor without dimensions (one number) is stored whole
+                    full.copy_(handles[file].get_tensor(name))
+                else:
+                    full[row:row + shape[0]].copy_(handles[file].get_tensor(name))
             params[path] = full
     finally:
         handles.clear()

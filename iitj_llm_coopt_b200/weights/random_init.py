@@ -52,7 +52,10 @@ def random_parameters(arch, spec, seed: int, engine_dtype: torch.dtype, std: flo
         if path not in params:
             params[path] = torch.empty(ps.shape, dtype=engine_dtype, device=device)
         piece = _draw(ps.kind, shape, seed, name, std, device).to(torch.bfloat16)
-        params[path][row:row + shape[0]].copy_(piece)
+        if not shape:
+            params[path].copy_(piece)
+        else:
+            params[path][row:row + shape[0]].copy_(piece)
         del piece
     return params
 

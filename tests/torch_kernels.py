@@ -92,6 +92,98 @@ def ref_silu_mul(gu):
     return torch.nn.functional.silu(g[:, :n]) * g[:, n:]
 
 
+
+def ref_conv_norm_store(u, bias, taps_w, q_gain, k_gain, state, state_slots, cu_seqlens, heads, kv_heads, head_dim,
+                        value_dim, eps, own_kv):
+    """The short convolution with its norms.  u [T, C]; state [slots, taps - 1, C] float32 or None (one tap).
+    Returns (q [T, H*D], k [T, G*D] | None, v [T, G*V] | None, new state rows {slot: [taps - 1, C]})."""
+    T, C = u.shape
+    n = taps_w.shape[1] if taps_w is not None else 1
+    x = u.float() + (bias.float() if bias is not None else 0)
+    y = torch.zeros_like(x)
+    new_state = {}
+    cu = [int(c) for c in cu_seqlens]
+    for b in range(len(cu) - 1):
+        lo, hi = cu[b], cu[b + 1]
+        slot = int(state_slots[b])
+        if n > 1:
+            full = torch.cat([state[slot].float(), x[lo:hi]])          # [n - 1 + rows, C]
+            y[lo:hi] = sum(taps_w[:, j].float() * full[j:j + hi - lo] for j in range(n))
+            new_state[slot] = full[-(n - 1):].clone()
+        else:
+            y[lo:hi] = x[lo:hi]
+    cq = heads * head_dim
+    def rms(z):
+        return z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + eps)
+    q = rms(y[:, :cq]) * q_gain.float()
+    if not own_kv:
+        return q, None, None, new_state
+    ck = kv_heads * head_dim
+    k = rms(y[:, cq:cq + ck]) * k_gain.float()
+    v = rms(y[:, cq + ck:].view(T, kv_heads, value_dim)).reshape(T, kv_heads * value_dim)
+    return q, k, v, new_state
+
+
+def ref_talking_attention(q, cache, block_table, token_request, positions, talk, slopes, heads, kv_heads, head_dim,
+                          value_dim, page_size, chunk, scale):
+    """q [T, H*D]; cache [pages, kv_heads*page*(D+V)] (key plane, then value plane); returns [T, H*V] float32."""
+    T = q.shape[0]
+    group = heads // kv_heads
+    kplane = cache[:, :kv_heads * page_size * head_dim].view(-1, kv_heads, page_size, head_dim)
+    vplane = cache[:, kv_heads * page_size * head_dim:].view(-1, kv_heads, page_size, value_dim)
+    out = torch.zeros(T, heads, value_dim, dtype=torch.float32, device=q.device)
+    for t in range(T):
+        pos = int(positions[t])
+        lo = (pos // chunk) * chunk if chunk > 0 else 0
+        idx = torch.arange(lo, pos + 1, device=q.device)
+        table = block_table[int(token_request[t])]
+        pages, offs = table[(idx // page_size).long()].long(), (idx % page_size).long()
+        k = kplane[pages, :, offs, :].float().repeat_interleave(group, dim=1)        # [n, H, D]
+        v = vplane[pages, :, offs, :].float().repeat_interleave(group, dim=1)        # [n, H, V]
+        qt = q[t].float().view(heads, head_dim)
+        s = torch.einsum("hd,nhd->hn", qt, k) * scale - slopes.float().view(heads, 1) * (pos - idx).float().view(1, -1)
+        a = talk.float() @ s
+        out[t] = torch.einsum("hn,nhv->hv", torch.softmax(a, dim=-1), v)
+    return out.view(T, heads * value_dim)
+
+
+def ref_retention(proj, cos, sin, rotary_dim, decay, state, state_slots, cu_seqlens, heads, head_dim, value_dim, k_scale):
+    """proj [T, q | k | v | ...]; state [slots, H, D, V] float32 (read, and returned updated as {slot: [H, D, V]});
+    returns (o [T, H*V] float32, new states)."""
+    T = proj.shape[0]
+    qk = heads * head_dim
+    q = proj[:, :qk].float().view(T, heads, head_dim).clone()
+    k = proj[:, qk:2 * qk].float().view(T, heads, head_dim).clone()
+    v = proj[:, 2 * qk:2 * qk + heads * value_dim].float().view(T, heads, value_dim)
+    if rotary_dim:
+        half = rotary_dim // 2
+        c, s = cos.float().view(T, 1, half), sin.float().view(T, 1, half)
+        for x in (q, k):
+            a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+            x[..., :half] = a * c - b * s
+            x[..., half:rotary_dim] = b * c + a * s
+    k = k * k_scale
+    o = torch.zeros(T, heads, value_dim, dtype=torch.float32, device=proj.device)
+    new = {}
+    cu = [int(c) for c in cu_seqlens]
+    d = decay.float().view(heads, 1, 1)
+    for b in range(len(cu) - 1):
+        slot = int(state_slots[b])
+        S = state[slot].float().clone()
+        for t in range(cu[b], cu[b + 1]):
+            S = d * S + k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        new[slot] = S
+    return o.view(T, heads * value_dim), new
+
+
+def ref_headnorm_gate(o, gate, heads, value_dim, eps):
+    T = o.shape[0]
+    x = o.float().view(T, heads, value_dim)
+    x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    return x.reshape(T, heads * value_dim) * torch.nn.functional.silu(gate.float())
+
+
 _M64 = np.uint64(0xFFFFFFFFFFFFFFFF)
 
 
@@ -165,6 +257,45 @@ class TorchKernels:
 
     def linear(self, x, weight, out, swiglu=False, defer=False):
         out.copy_(ref_linear(x, weight, swiglu))     # never split: `defer` has nothing to leave for later
+        return out
+
+    def conv_norm_store(self, u, bias, taps_w, q_gain, k_gain, state, state_slots, token_request, cu_seqlens, q_out,
+                        cache, slots, heads, kv_heads, head_dim, value_dim, eps):
+        own = cache is not None
+        q, k, v, new = ref_conv_norm_store(u, bias, taps_w, q_gain, k_gain, state, state_slots, cu_seqlens, heads,
+                                           kv_heads, head_dim, value_dim, eps, own)
+        q_out.copy_(q)
+        if own:
+            ps = cache.shape[1] // (kv_heads * (head_dim + value_dim))
+            kplane = cache[:, :kv_heads * ps * head_dim].view(-1, kv_heads, ps, head_dim)
+            vplane = cache[:, kv_heads * ps * head_dim:].view(-1, kv_heads, ps, value_dim)
+            for t in range(u.shape[0]):
+                p, o = divmod(int(slots[t]), ps)
+                kplane[p, :, o, :] = k[t].view(kv_heads, head_dim).to(cache.dtype)
+                vplane[p, :, o, :] = v[t].view(kv_heads, value_dim).to(cache.dtype)
+        for slot, rows in new.items():
+            state[slot] = rows
+        return q_out
+
+    def talking_attention(self, q, cache, meta, talk, slopes, out, heads, kv_heads, head_dim, value_dim, chunk, scale):
+        ps = cache.shape[1] // (kv_heads * (head_dim + value_dim))
+        out.copy_(ref_talking_attention(q, cache, meta.block_table, meta.token_request, meta.positions, talk, slopes,
+                                        heads, kv_heads, head_dim, value_dim, ps, chunk, scale))
+        return out
+
+    def retention(self, proj, tables, rotary_dim, decay, state, state_slots, cu_seqlens, o, heads, head_dim, value_dim,
+                  k_scale, write=True):
+        cos, sin = tables if tables is not None else (None, None)
+        got, new = ref_retention(proj, cos, sin, rotary_dim, decay, state, state_slots, cu_seqlens, heads, head_dim,
+                                 value_dim, k_scale)
+        o.copy_(got)
+        if write:
+            for slot, S in new.items():
+                state[slot] = S
+        return o
+
+    def headnorm_gate(self, o, proj, gate_col, out, heads, value_dim, eps):
+        out.copy_(ref_headnorm_gate(o, proj[:, gate_col:gate_col + heads * value_dim], heads, value_dim, eps))
         return out
 
     health_codes = (0, 0, 0, 0)     # what `sample` reports as the library's health words (tests set a failure here)
