@@ -5,7 +5,7 @@ Keys: "architecture" ("Lifusun"), "width", "vocab", "norm" {"eps"} and "layers",
 ({"kind": "dense", "ff": inner width}, or null for a layer without one).
 
 An attention mixer: "heads", "kv_heads", "dim" (query/key head size), "vdim" (value head size), "scale" (of the
-scores), "conv" (taps of the short convolution over time on q, k and v), "mask" {"size"} (queries see keys of
+scores), "conv" (taps of the short convolution over time on q, k and v; absent: none), "mask" {"size"} (queries see keys of
 their own chunk of that many positions) and optionally "kv_from" (the index of an earlier attention layer whose
 cached keys and values this layer reads; it then has no key/value tensors of its own).
 A retention mixer: "heads", "dim", "vdim", "decay" (one per head) and "rot" {"dims", "base"} (the leading dims of
@@ -72,12 +72,12 @@ class LifusunConfig:
             where = f"layers[{i}]"
             kind, m = _get(layer, "type", where), _get(layer, "mixer", where)
             if kind == "attention":
-                for k in ("heads", "kv_heads", "dim", "vdim", "scale", "conv"):
+                for k in ("heads", "kv_heads", "dim", "vdim", "scale"):
                     _get(m, k, where + ".mixer")
                 if m["heads"] % m["kv_heads"]:
                     raise ConfigError(f"{where}: heads {m['heads']} is not a multiple of kv_heads {m['kv_heads']}")
-                if int(m["conv"]) < 1 or int(m["conv"]) > 8:
-                    raise ConfigError(f"{where}: conv {m['conv']} taps are not supported (1 to 8)")
+                if not 0 <= int(m.get("conv") or 0) <= 8:
+                    raise ConfigError(f"{where}: conv {m['conv']} taps are not supported (up to 8)")
                 if m.get("mask") is not None and int(_get(m["mask"], "size", where + ".mixer.mask")) <= 0:
                     raise ConfigError(f"{where}: mask.size must be positive")
                 if m.get("kv_from") is not None:
@@ -123,10 +123,10 @@ class LifusunConfig:
                 mask = m.get("mask") or {}
                 mixer = MixerSpec(kind="talking_attention", width=self.width, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]),
                                   head_dim=int(m["dim"]), value_dim=int(m["vdim"]), softmax_scale=float(m["scale"]),
-                                  options=(("bias", True), ("chunk", int(mask.get("size", 0))), ("conv_taps", int(m["conv"])),
+                                  options=(("bias", True), ("chunk", int(mask.get("size", 0))), ("conv_taps", int(m.get("conv") or 0)),
                                            ("eps", self.eps), ("own_kv", shared is None), ("slope_exponent", 8.0)))
                 order.append(LayerCall(layer=i, cache=i if shared is None else int(shared), write=shared is None,
-                                       state=n + i if int(m["conv"]) > 1 else None))
+                                       state=n + i if int(m.get("conv") or 0) > 1 else None))
             else:
                 rot = m.get("rot") or {"dims": 0, "base": 10000.0}
                 pos = PositionSpec(kind="rope", head_dim=int(m["dim"]), rotary_dim=int(rot["dims"]), theta=float(rot["base"]),

@@ -38,7 +38,7 @@ conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, 
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
         const float bc = bias ? bias[c] : 0.f;
         float acc = 0.f;
-        if (taps > 1) {
+        if (taps_w) {
             for (int j = 0; j < taps; ++j) {
                 const int src = local - (back - j);
                 const float x = src >= 0 ? to_f32(u[(size_t)(t - (back - j)) * channels + c]) + bc
@@ -122,6 +122,7 @@ LLM_API int llm_conv_norm_store(const void* u, const float* bias, const float* t
     if (tokens == 0) return 0;
     if (taps < 1 || taps > kMaxTaps) LLM_FAIL(-1, "short convolution: %d taps are not supported (1 to %d)", taps, kMaxTaps);
     if (taps > 1 && (!state || !taps_w)) LLM_FAIL(-1, "short convolution: %d taps need weights and a state", taps);
+    if (!taps_w) taps = 1;
     const int channels = heads * dim + (cache ? kv_heads * (dim + vdim) : 0);
     const size_t smem = (size_t)channels * sizeof(float);
     if (smem > 200 * 1024) LLM_FAIL(-1, "short convolution: %d channels do not fit shared memory", channels);

@@ -3,7 +3,7 @@ causal convolution over time on the projections, norms on queries, keys and valu
 of a rotation, and an optional chunked mask.  Every constant is a parameter of the spec.
 
     u   = x W^T + b                         (q, k and v as one product; b when `bias`)
-    c_t = sum_j taps[:, j] * u_(t - n + 1 + j)      n = `conv_taps`; zeros before the request's first token; the
+    c_t = sum_j taps[:, j] * u_(t - n + 1 + j)      n = `conv_taps` (0: c = u); zeros before the request's first token; the
                                             last n - 1 rows of u of every request are its convolution state
     q   = rmsnorm(c_q over all query heads at once) * q_gain,    k likewise with k_gain,
     v   = each value head of c_v divided by its root mean square (no gain);   k and v are what the cache holds
@@ -37,7 +37,7 @@ class TalkingAttention(Part):
         if self.heads % self.kv_heads:
             raise ValueError(f"talking attention: heads {self.heads} is not a multiple of kv_heads {self.kv_heads}")
         self.scale = spec.softmax_scale or self.head_dim ** -0.5
-        self.chunk, self.taps = int(spec.option("chunk", 0)), int(spec.option("conv_taps", 1))
+        self.chunk, self.taps = int(spec.option("chunk", 0)), int(spec.option("conv_taps", 0))      # 0 taps: no convolution
         self.bias, self.own_kv = bool(spec.option("bias", False)), bool(spec.option("own_kv", True))
         self.eps = float(spec.option("eps", 1e-6))
         self.channels = self._channels(spec)
@@ -67,7 +67,7 @@ class TalkingAttention(Part):
                "o": ParamSpec((spec.width, spec.heads * (spec.value_dim or spec.head_dim)))}
         if spec.option("bias", False):
             out["qkv_bias"] = ParamSpec((c,), kind="vector", pieces=rows)
-        if int(spec.option("conv_taps", 1)) > 1:
+        if int(spec.option("conv_taps", 0)) >= 1:
             out["qkv_conv"] = ParamSpec((c, int(spec.option("conv_taps"))), kind="vector", pieces=rows)
         if spec.option("own_kv", True):
             out["k_norm"] = ParamSpec((spec.kv_heads * spec.head_dim,), kind="vector")
@@ -80,7 +80,7 @@ class TalkingAttention(Part):
 
     @classmethod
     def state_need(cls, spec) -> CacheNeed:
-        return CacheNeed(kind="state", state_shape=(int(spec.option("conv_taps", 1)) - 1, cls._channels(spec)),
+        return CacheNeed(kind="state", state_shape=(max(int(spec.option("conv_taps", 0)) - 1, 0), cls._channels(spec)),
                          state_dtype="float32")
 
     def load(self, tensors: dict) -> None:

@@ -106,10 +106,11 @@ def ref_conv_norm_store(u, bias, taps_w, q_gain, k_gain, state, state_slots, cu_
     for b in range(len(cu) - 1):
         lo, hi = cu[b], cu[b + 1]
         slot = int(state_slots[b])
-        if n > 1:
-            full = torch.cat([state[slot].float(), x[lo:hi]])          # [n - 1 + rows, C]
+        if taps_w is not None:
+            full = torch.cat([state[slot].float(), x[lo:hi]]) if n > 1 else x[lo:hi]          # [n - 1 + rows, C]
             y[lo:hi] = sum(taps_w[:, j].float() * full[j:j + hi - lo] for j in range(n))
-            new_state[slot] = full[-(n - 1):].clone()
+            if n > 1:
+                new_state[slot] = full[-(n - 1):].clone()
         else:
             y[lo:hi] = x[lo:hi]
     cq = heads * head_dim
