@@ -1,94 +1,242 @@
 // Retention: linear attention with a fixed decay per head, as a scan over each request's tokens.
 //     S_t = decay_h * S_(t-1) + k_t v_t^T,     o_t = S_t^T q_t         S [dim, vdim] float32 per request and head
 // q and k are rotated on their leading `2 * half` dims (pairs (i, i + half), angles from float32 cos/sin tables of
-// the step's positions) and k is scaled, all in float32, as the rows are staged in shared memory.
+// the step's positions) and k is scaled, all in float32, by a kernel of its own ahead of the walk.
 //
 // The columns of S evolve independently (column c needs v_t[c] only), so a block owns `cpb` columns of one head of
 // one request and walks the request's tokens in order; the `dim` rows of a column are shared out over `ds` neighbouring
-// lanes (each keeps up to kRows of them in registers) whose partial outputs a shuffle adds.  The walk is the same
-// whatever the step's cut, so a portion continues bit for bit where the one before it stopped.
+// lanes (each keeps R of them in registers) whose partial outputs a shuffle adds.  The launcher picks R (and so the
+// number of blocks, vdim / cpb per head and request) so that the grid fills the machine: the walk itself cannot be cut.
+// The rows of the next block of tokens travel to shared memory (cp.async) while the current block is walked.
+// Measured on B200 (2,048 tokens of one request, 32 heads): head sizes 64 / 64: 0.63 ms in segments, head sizes 128 / 128:
+// 1.7 ms whole.  What bounds it is the count of instructions a token costs a warp (about a hundred for 24 useful
+// multiply-adds at eight rows a thread: addresses from the run-time lane split, the shuffles of the sum), not memory.
+// The walk is the same whatever the step's cut, so a portion continues bit for bit where the one before it stopped.
+//
+// A long portion is walked in two passes so that the walk is cut after all: pass one walks segments of `seg_len` tokens
+// side by side, each from zero (a request's first from its state), and leaves what each gathered; pass two gives every
+// later segment the state that stood at its start, S_in = sum over earlier segments of decay^(tokens in between) * gathered,
+// adds decay^(n + 1) * S_in^T q to its n-th token, and the request's last segment leaves the state.  Where segments are
+// cut depends on where the portion starts, which moves results by rounding only.
+//
+// The state is kept transposed, [slot, head, vdim, dim], so that the lanes that share a column read neighbouring words.
 //
 // `retention_headnorm_gate` then divides every head of o by its root mean square and multiplies by silu(gate).
 #include "common.cuh"
 
 namespace {
 
-constexpr int kRows = 32;
+constexpr int kThreads = 128;
+constexpr int kTargetBlocks = 2 * 148;
+constexpr int kTokenBlock = 16;
+constexpr int kSegment = 128;        // tokens of a segment, about (see the launcher)
+constexpr int kMaxSegments = 32;
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// q and k of every token and head, rotated and (k) scaled, as float32 [tokens, heads, 2, dim]: done once, ahead of the
+// walk, so that the blocks that share a head's rows (one per `cpb` columns) do not each rotate them again.
 template <typename T>
 __global__ void __launch_bounds__(128)
-retention_scan_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ cos_t,
-                      const float* __restrict__ sin_t, int half, const float* __restrict__ decay,
-                      float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
-                      float* __restrict__ out, int heads, int dim, int vdim, int ds, int cpb, int tb, float k_scale,
-                      int write) {
+retention_rotate_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, int half, float* __restrict__ qk, int heads, int dim,
+                        float k_scale, long long rows) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float smem[];
-    float* qs = smem;                    // [tb, dim]
-    float* ks = qs + tb * dim;           // [tb, dim]
-    float* vs = ks + tb * dim;           // [tb, cpb]
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int s = threadIdx.x % ds, cl = threadIdx.x / ds;
-    const int c = blockIdx.x * cpb + cl;
-    const bool live = cl < cpb && c < vdim;
-    const int begin = cu_seqlens[b], end = cu_seqlens[b + 1];
-    const float dec = decay[h];
-    float* st = state + ((size_t)state_slots[b] * heads + h) * dim * vdim;
-    float S[kRows];
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-        const int d = s + ds * r;
-        S[r] = (live && d < dim) ? st[(size_t)d * vdim + c] : 0.f;
-    }
+    const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);     // (token, head)
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = row / heads;
+    const int h = (int)(row % heads);
+    const T* q = proj + (size_t)t * proj_stride + (size_t)h * dim;
+    const T* k = q + (size_t)heads * dim;
+    float* dst = qk + (size_t)row * 2 * dim;
     const int rot = 2 * half;
-    const size_t q_col = (size_t)h * dim, k_col = (size_t)heads * dim + (size_t)h * dim;
-    const size_t v_col = 2 * (size_t)heads * dim + (size_t)h * vdim;
-    for (int t0 = begin; t0 < end; t0 += tb) {
-        const int nb = min(tb, end - t0);
-        for (int idx = threadIdx.x; idx < nb * dim; idx += blockDim.x) {
-            const int tt = idx / dim, d = idx % dim;
-            const T* row = proj + (size_t)(t0 + tt) * proj_stride;
-            float qv = to_f32(row[q_col + d]), kv = to_f32(row[k_col + d]);
-            if (d < rot) {
-                const bool first = d < half;
-                const int i = first ? d : d - half, pd = first ? d + half : d - half;
-                const float cs = cos_t[(size_t)(t0 + tt) * half + i], sn = sin_t[(size_t)(t0 + tt) * half + i];
-                const float qp = to_f32(row[q_col + pd]), kp = to_f32(row[k_col + pd]);
-                qv = first ? qv * cs - qp * sn : qv * cs + qp * sn;
-                kv = first ? kv * cs - kp * sn : kv * cs + kp * sn;
-            }
-            qs[idx] = qv;
-            ks[idx] = kv * k_scale;
+    for (int d = lane; d < dim; d += 32) {
+        float qv = to_f32(q[d]), kv = to_f32(k[d]);
+        if (d < rot) {
+            const bool first = d < half;
+            const int i = first ? d : d - half, pd = first ? d + half : d - half;
+            const float cs = cos_t[(size_t)t * half + i], sn = sin_t[(size_t)t * half + i];
+            const float qp = to_f32(q[pd]), kp = to_f32(k[pd]);
+            qv = first ? qv * cs - qp * sn : qv * cs + qp * sn;
+            kv = first ? kv * cs - kp * sn : kv * cs + kp * sn;
         }
+        dst[d] = qv;
+        dst[dim + d] = kv * k_scale;
+    }
+}
+
+// Rows [t0, t0 + nb) of the rotated q and k of head h (float32, `dim` each) and of this block's `cpb` value columns (as
+// stored) into one stage: qs [tb, dim], ks [tb, dim] float32, then raw values [tb, cpb].
+template <typename T>
+__device__ __forceinline__ void stage_rows(float* qs, float* ks, T* rawv, const float* __restrict__ qk, const T* __restrict__ proj,
+                                           int proj_stride, int heads, int h, int t0, int nb, int dim, int cpb, size_t v_col,
+                                           int vcols, bool vec_qk, bool vec_v) {
+    constexpr int kPer = 16 / (int)sizeof(T);
+    if (vec_qk) {
+        const int per_row = dim / 4;             // 16-byte pieces of a row; a token's q row and k row follow each other
+        for (int idx = threadIdx.x; idx < nb * 2 * per_row; idx += blockDim.x) {
+            const int tt = idx / (2 * per_row), x = idx % (2 * per_row);
+            const float* src = qk + ((size_t)(t0 + tt) * heads + h) * 2 * dim + (size_t)x * 4;
+            float* dst = x < per_row ? qs + tt * dim + x * 4 : ks + tt * dim + (x - per_row) * 4;
+            cp_async16(dst, src);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < nb * 2 * dim; idx += blockDim.x) {
+            const int tt = idx / (2 * dim), x = idx % (2 * dim);
+            const float v = qk[((size_t)(t0 + tt) * heads + h) * 2 * dim + x];
+            if (x < dim) qs[tt * dim + x] = v;
+            else ks[tt * dim + x - dim] = v;
+        }
+    }
+    if (vec_v) {
+        const int vper = cpb / kPer;
+        for (int idx = threadIdx.x; idx < nb * vper; idx += blockDim.x) {
+            const int tt = idx / vper, x = (idx % vper) * kPer;
+            cp_async16(rawv + tt * cpb + x, proj + (size_t)(t0 + tt) * proj_stride + v_col + x);
+        }
+    } else {
         for (int idx = threadIdx.x; idx < nb * cpb; idx += blockDim.x) {
-            const int tt = idx / cpb, cc = blockIdx.x * cpb + idx % cpb;
-            vs[idx] = cc < vdim ? to_f32(proj[(size_t)(t0 + tt) * proj_stride + v_col + cc]) : 0.f;
+            const int tt = idx / cpb, x = idx % cpb;
+            rawv[tt * cpb + x] = x < vcols ? proj[(size_t)(t0 + tt) * proj_stride + v_col + x] : from_f32<T>(0.f);
         }
+    }
+    cp_async_commit();
+}
+
+// MODE 0 walks; MODE 1 is the second pass of a walk that was cut into segments (see the launcher).
+template <typename T, int R, int MODE>
+__global__ void __launch_bounds__(kThreads)
+retention_scan_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ qk,
+                      const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
+                      float* __restrict__ out, int heads, int dim, int vdim, int ds, int cpb, int write, int vec,
+                      int nseg, int seg_len, float* __restrict__ seg_state) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    constexpr int tb = kTokenBlock;
+    // two stages of: q rows [tb, dim], k rows [tb, dim] (float32, as the rotation left them), value columns [tb, cpb] as stored
+    const size_t stage_bytes = sizeof(float) * 2 * tb * dim + sizeof(T) * tb * cpb;
+    float* vs = reinterpret_cast<float*>(smem_bytes + 2 * stage_bytes);        // [tb, cpb] float32
+    const int h = blockIdx.y;
+    // segment `seg` of request b: MODE 0 has a block for each, MODE 1 for all but a request's first
+    const int b = MODE == 0 ? blockIdx.z / nseg : blockIdx.z / (nseg - 1);
+    const int seg = MODE == 0 ? blockIdx.z % nseg : blockIdx.z % (nseg - 1) + 1;
+    const int s = threadIdx.x % ds, cl = threadIdx.x / ds;
+    const int c0 = blockIdx.x * cpb;
+    const int c = c0 + cl;
+    const bool live = c < vdim;
+    const int vcols = min(cpb, vdim - c0);
+    const bool vvec = vec && vcols == cpb;
+    const int req_begin = cu_seqlens[b], req_end = cu_seqlens[b + 1];
+    const int begin = nseg > 1 ? min(req_end, req_begin + seg * seg_len) : req_begin;
+    const int end = nseg > 1 ? min(req_end, begin + seg_len) : req_end;
+    if (begin >= end) return;                // the request is shorter than this segment's start (the whole block leaves)
+    const float dec = decay[h];
+    float* st = state + (((size_t)state_slots[b] * heads + h) * vdim + (live ? c : 0)) * dim;
+    // where segment j of this (request, head, column) leaves what it gathered from zero (segment 0: from the state)
+    float* sg = seg_state ? seg_state + ((((size_t)b * nseg) * heads + h) * vdim + (live ? c : 0)) * dim : nullptr;
+    const size_t sg_stride = (size_t)heads * vdim * dim;
+    float S[R];
+    if (MODE == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = s + ds * r;
+            S[r] = (live && d < dim && seg == 0) ? st[d] : 0.f;
+        }
+    } else {
+        // the state at this segment's start: what the segments before it gathered, each decayed over those after it
+        const float dl = powf(dec, (float)seg_len);
+#pragma unroll
+        for (int r = 0; r < R; ++r) S[r] = 0.f;
+        for (int j = 0; j < seg; ++j) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = s + ds * r;
+                if (live && d < dim) S[r] = fmaf(dl, S[r], sg[(size_t)j * sg_stride + d]);
+            }
+        }
+    }
+    const size_t v_col = 2 * (size_t)heads * dim + (size_t)h * vdim + c0;
+    const bool vec_qk = dim % 4 == 0;
+    auto stage_q = [&](int st_) { return reinterpret_cast<float*>(smem_bytes + st_ * stage_bytes); };
+    auto stage_v = [&](int st_) { return reinterpret_cast<T*>(smem_bytes + st_ * stage_bytes + sizeof(float) * 2 * tb * dim); };
+    stage_rows<T>(stage_q(0), stage_q(0) + tb * dim, stage_v(0), qk, proj, proj_stride, heads, h, begin, min(tb, end - begin), dim, cpb,
+                  v_col, vcols, vec_qk, vvec);
+    int stage = 0;
+    float carried = 1.f;
+    for (int t0 = begin; t0 < end; t0 += tb, stage ^= 1) {
+        const int nb = min(tb, end - t0);
+        const float* qs = stage_q(stage);
+        const float* ks = qs + tb * dim;
+        const T* rawv = stage_v(stage);
+        cp_async_wait_all();
+        __syncthreads();                     // the staged rows have landed; everybody is done with the other stage and with vs
+        if (t0 + tb < end)                   // the next block's rows travel while this one is walked
+            stage_rows<T>(stage_q(stage ^ 1), stage_q(stage ^ 1) + tb * dim, stage_v(stage ^ 1), qk, proj, proj_stride, heads, h, t0 + tb,
+                          min(tb, end - t0 - tb), dim, cpb, v_col, vcols, vec_qk, vvec);
+        for (int idx = threadIdx.x; idx < nb * cpb; idx += blockDim.x)
+            vs[idx] = (idx % cpb) < vcols ? to_f32(rawv[idx]) : 0.f;
         __syncthreads();
         for (int tt = 0; tt < nb; ++tt) {
-            const float vv = cl < cpb ? vs[tt * cpb + cl] : 0.f;
-            const float* kr = ks + tt * dim;
             const float* qr = qs + tt * dim;
             float part = 0.f;
+            if (MODE == 0) {
+                const float vv = vs[tt * cpb + cl];
+                const float* kr = ks + tt * dim;
 #pragma unroll
-            for (int r = 0; r < kRows; ++r) {
-                const int d = s + ds * r;
-                if (d < dim) {
-                    S[r] = fmaf(dec, S[r], kr[d] * vv);
-                    part = fmaf(S[r], qr[d], part);
+                for (int r = 0; r < R; ++r) {
+                    const int d = s + ds * r;
+                    if (d < dim) {
+                        S[r] = fmaf(dec, S[r], kr[d] * vv);
+                        part = fmaf(S[r], qr[d], part);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int d = s + ds * r;
+                    if (d < dim) part = fmaf(S[r], qr[d], part);
                 }
             }
             for (int o = ds >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (live && s == 0) out[(size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c] = part;
+            float* o_at = out + (size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c;
+            if (MODE == 0) {
+                if (live && s == 0) *o_at = part;
+            } else {
+                carried *= dec;              // decay^(tokens of this segment up to and including this one)
+                if (live && s == 0) *o_at += carried * part;
+            }
         }
-        __syncthreads();
     }
-    if (write && live) {
+    if (!live) return;
+    if (MODE == 0) {
+        if (nseg > 1) {
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
+            for (int r = 0; r < R; ++r) {
+                const int d = s + ds * r;
+                if (d < dim) sg[(size_t)seg * sg_stride + d] = S[r];
+            }
+        }
+        // a request of one segment is done after this pass
+        if (write && seg == 0 && end == req_end) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = s + ds * r;
+                if (d < dim) st[d] = S[r];
+            }
+        }
+    } else if (write && end == req_end) {
+        // the request's last segment leaves the state: what stood at its start, decayed over it, and what it gathered
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
             const int d = s + ds * r;
-            if (d < dim) st[(size_t)d * vdim + c] = S[r];
+            if (d < dim) st[d] = fmaf(carried, S[r], sg[(size_t)seg * sg_stride + d]);
         }
     }
 }
@@ -120,29 +268,79 @@ headnorm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, in
 }  // namespace
 
 // proj [tokens, proj_stride]: q of all heads, then k, then v (heads * vdim).  cos_t / sin_t [tokens, half] float32 (half = 0:
-// no rotation).  state [slots, heads, dim, vdim] float32; out [tokens, heads * vdim] float32.
+// no rotation).  state [slots, heads, vdim, dim] float32 (transposed); out [tokens, heads * vdim] float32.
+// `longest`: the most tokens one request brings; `seg_state`: scratch of `seg_state_floats` floats for the two-pass form
+// (null: one pass); `qk_scratch`: tokens * heads * 2 * dim floats for the rotated q and k.  Returns the number of segments
+// (1: one pass) or a negative code.
 LLM_API int llm_retention_scan(const void* proj, int proj_stride, const float* cos_t, const float* sin_t, int half,
                                const float* decay, float* state, const int* state_slots, const int* cu_seqlens,
                                float* out, int dtype, int tokens, int requests, int heads, int dim, int vdim, float k_scale,
-                               int write, cudaStream_t stream) {
+                               int write, int longest, float* seg_state, long long seg_state_floats, float* qk_scratch,
+                               cudaStream_t stream) {
     if (tokens == 0 || requests == 0) return 0;
-    int ds = 1;
-    while ((dim + ds - 1) / ds > kRows) ds *= 2;
-    if (ds > 32) LLM_FAIL(-1, "retention: head size %d is too large (at most %d)", dim, 32 * kRows);
     if (2 * half > dim) LLM_FAIL(-1, "retention: %d rotated dims exceed the head size %d", 2 * half, dim);
-    const int unit = 32 / ds;                                   // columns of one warp
-    int cpb = 128 / ds;
-    const int need = (vdim + unit - 1) / unit * unit;           // whole warps
-    if (need < cpb) cpb = need;
-    const int tb = dim <= 256 ? 16 : (dim <= 512 ? 8 : 4);
-    const size_t smem = sizeof(float) * ((size_t)2 * tb * dim + (size_t)tb * cpb);
+    if (dim > 1024) LLM_FAIL(-1, "retention: head size %d is too large (at most 1024)", dim);
+    // segments: only where a request brings several hundred tokens and the walk as a whole has too few blocks for the machine
+    // (two passes cost twice the arithmetic); as many as `seg_state` has room for
+    int nseg = 1, seg_len = 0;
+    int min_ds = 1;
+    while (min_ds * 4 < dim && min_ds < 32) min_ds *= 2;       // lanes per column at the fewest rows a thread takes
+    const long long whole_blocks = (long long)requests * heads * ((vdim + kThreads / min_ds - 1) / (kThreads / min_ds));
+    if (longest >= 2 * kSegment && seg_state && whole_blocks < kTargetBlocks) {
+        nseg = (longest + kSegment - 1) / kSegment;
+        if (nseg > kMaxSegments) nseg = kMaxSegments;
+        seg_len = ((longest + nseg - 1) / nseg + kTokenBlock - 1) / kTokenBlock * kTokenBlock;
+        nseg = (longest + seg_len - 1) / seg_len;
+        if ((long long)requests * nseg * heads * vdim * dim > seg_state_floats) nseg = 1;
+    }
+    // rows per thread: as many as still give the machine enough blocks (fewer rows = more lanes per column = more blocks)
+    int rows = 32, ds = 1, cpb = kThreads;
+    for (;; rows /= 2) {
+        ds = 1;
+        while (ds * rows < dim) ds *= 2;
+        if (ds <= 32) {
+            cpb = kThreads / ds;
+            const long long blocks = (long long)requests * nseg * heads * ((vdim + cpb - 1) / cpb);
+            if (blocks >= kTargetBlocks || rows == 4 || ds == 32) break;
+        }
+        if (rows == 4) break;
+    }
+    if (ds > 32) LLM_FAIL(-1, "retention: head size %d does not fit", dim);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        llm_launch(retention_scan_kernel<T>, dim3((vdim + cpb - 1) / cpb, heads, requests), cpb * ds, smem, stream,
-                   (const T*)proj, proj_stride, cos_t, sin_t, half, decay, state, state_slots, cu_seqlens, out, heads, dim,
-                   vdim, ds, cpb, tb, k_scale, write);
+        constexpr int kPer = 16 / (int)sizeof(T);
+        const int vec = (dim % kPer == 0 && vdim % kPer == 0 && cpb % kPer == 0 && proj_stride % kPer == 0 &&
+                         ((size_t)proj % 16) == 0) ? 1 : 0;                 // the value columns travel in 16-byte pieces
+        const size_t smem = 2 * (sizeof(float) * 2 * kTokenBlock * dim + sizeof(T) * kTokenBlock * cpb) + sizeof(float) * kTokenBlock * cpb;
+        const long long rows_qk = (long long)tokens * heads;
+        llm_launch(retention_rotate_kernel<T>, (unsigned)((rows_qk + 3) / 4), 128, 0, stream, (const T*)proj, proj_stride, cos_t, sin_t,
+                   half, qk_scratch, heads, dim, k_scale, rows_qk);
+        LLM_CHECK_LAUNCH("retention_rotate");
+        const unsigned gx = (vdim + cpb - 1) / cpb;
+#define LLM_RET(RR, MODE, GZ)                                                                                              \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024)                                                                                              \
+            cudaFuncSetAttribute(retention_scan_kernel<T, RR, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        llm_launch(retention_scan_kernel<T, RR, MODE>, dim3(gx, heads, GZ), kThreads, smem, stream, (const T*)proj, proj_stride,  \
+                   (const float*)qk_scratch, decay, state, state_slots, cu_seqlens, out, heads, dim, vdim, ds, cpb, write,  \
+                   vec, nseg, seg_len, nseg > 1 ? seg_state : (float*)nullptr);                                           \
+    } while (0)
+#define LLM_RET_ROWS(MODE, GZ)                   \
+    do {                                         \
+        if (rows == 32) LLM_RET(32, MODE, GZ);   \
+        else if (rows == 16) LLM_RET(16, MODE, GZ); \
+        else if (rows == 8) LLM_RET(8, MODE, GZ);  \
+        else LLM_RET(4, MODE, GZ);               \
+    } while (0)
+        LLM_RET_ROWS(0, requests * nseg);
         LLM_CHECK_LAUNCH("retention_scan");
-        return 0;
+        if (nseg > 1) {
+            LLM_RET_ROWS(1, requests * (nseg - 1));
+            LLM_CHECK_LAUNCH("retention_scan (second pass)");
+        }
+#undef LLM_RET_ROWS
+#undef LLM_RET
+        return nseg;
     });
 }
 

@@ -15,6 +15,17 @@ namespace {
 
 constexpr int kMaxTaps = 8;
 
+__device__ __forceinline__ void load2(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x;
+    b = v.y;
+}
+__device__ __forceinline__ void load2(const __nv_bfloat16* p, float& a, float& b) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    a = v.x;
+    b = v.y;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, const float* __restrict__ taps_w, int taps,
@@ -35,22 +46,62 @@ conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, 
     const float* st = state ? state + (size_t)state_slots[b] * back * channels : nullptr;
     const int cq = heads * dim, ck = cache ? kv_heads * dim : 0;
     float ssq = 0.f, ssk = 0.f;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        const float bc = bias ? bias[c] : 0.f;
-        float acc = 0.f;
-        if (taps_w) {
-            for (int j = 0; j < taps; ++j) {
-                const int src = local - (back - j);
-                const float x = src >= 0 ? to_f32(u[(size_t)(t - (back - j)) * channels + c]) + bc
-                                         : st[(size_t)(back + src) * channels + c];
-                acc = fmaf(taps_w[(size_t)c * taps + j], x, acc);
+    if (channels % 2 == 0 && cq % 2 == 0 && ck % 2 == 0) {
+        // two neighbouring channels per thread and load; the taps' loads of a pair are all asked for before the first is used
+        for (int c = 2 * threadIdx.x; c < channels; c += 2 * blockDim.x) {
+            const float b0 = bias ? bias[c] : 0.f, b1 = bias ? bias[c + 1] : 0.f;
+            float x0[kMaxTaps], x1[kMaxTaps];
+#pragma unroll
+            for (int j = 0; j < kMaxTaps; ++j) {
+                if (j < taps) {
+                    const int src = local - (back - j);
+                    if (src >= 0) {
+                        load2(u + (size_t)(t - (back - j)) * channels + c, x0[j], x1[j]);
+                        x0[j] += b0;
+                        x1[j] += b1;
+                    } else {
+                        const float2 v = *reinterpret_cast<const float2*>(st + (size_t)(back + src) * channels + c);
+                        x0[j] = v.x;
+                        x1[j] = v.y;
+                    }
+                }
             }
-        } else {
-            acc = to_f32(u[(size_t)t * channels + c]) + bc;
+            float a0 = 0.f, a1 = 0.f;
+            if (taps_w) {
+#pragma unroll
+                for (int j = 0; j < kMaxTaps; ++j) {
+                    if (j < taps) {
+                        a0 = fmaf(taps_w[(size_t)c * taps + j], x0[j], a0);
+                        a1 = fmaf(taps_w[(size_t)(c + 1) * taps + j], x1[j], a1);
+                    }
+                }
+            } else {
+                a0 = x0[0];
+                a1 = x1[0];
+            }
+            y[c] = a0;
+            y[c + 1] = a1;
+            if (c < cq) ssq += a0 * a0 + a1 * a1;
+            else if (c < cq + ck) ssk += a0 * a0 + a1 * a1;
         }
-        y[c] = acc;
-        if (c < cq) ssq += acc * acc;
-        else if (c < cq + ck) ssk += acc * acc;
+    } else {
+        for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+            const float bc = bias ? bias[c] : 0.f;
+            float acc = 0.f;
+            if (taps_w) {
+                for (int j = 0; j < taps; ++j) {
+                    const int src = local - (back - j);
+                    const float x = src >= 0 ? to_f32(u[(size_t)(t - (back - j)) * channels + c]) + bc
+                                             : st[(size_t)(back + src) * channels + c];
+                    acc = fmaf(taps_w[(size_t)c * taps + j], x, acc);
+                }
+            } else {
+                acc = to_f32(u[(size_t)t * channels + c]) + bc;
+            }
+            y[c] = acc;
+            if (c < cq) ssq += acc * acc;
+            else if (c < cq + ck) ssk += acc * acc;
+        }
     }
     const float tq = block_sum(ssq, red);
     const float inv_q = 1.0f / sqrtf(tq / (float)cq + eps);

@@ -1,0 +1,207 @@
+"""A model family beside the Llama of the same layer sizes (`bench.py --family NAME --shape SIZE`).
+
+Both models get the same width, inner width, head counts, head size, vocabulary and depth (eight layers), random
+weights, and run through the same engine: one prompt of `prefill_tokens` tokens in one step, and decode steps of
+`batch` requests with `context` tokens each in the cache, timed on the device with CUDA events (three or more
+warm-up runs, a write of 256 MB between prefill runs so that nothing of the run before is left in L2; a decode step
+reads more weights than L2 holds).  Then the family's own kernels alone, at the shapes they have in those steps,
+each with the bytes it must move and the fraction of the copy bandwidth that is, beside the Llama kernels that do
+the like work (rotation and cache store for the convolution kernel, prefill and decode attention).
+"""
+from __future__ import annotations
+
+import statistics
+import time
+from types import SimpleNamespace
+
+
+def _timed(fn, reps, warmup, flush=None):
+    import torch
+    times = []
+    for it in range(warmup + reps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        if flush is not None:
+            flush.add_(1.0)          # runs just before the timed work, so the launch's way to the GPU is not in the time
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def _engine(config_dict, page, pool_tokens, max_seqs, step_tokens, graphs):
+    from . import LLM
+    from .config.registry import architecture_for
+    typed = architecture_for(config_dict).config_class.from_dict(config_dict)
+    return LLM(config=typed, random_seed=3, dtype="bfloat16", page_size=page, num_pages=-(-pool_tokens // page),
+               max_num_seqs=max_seqs, max_num_batched_tokens=step_tokens, max_model_len=1 << 20, cuda_graphs=graphs)
+
+
+def _model_runs(name, config_dict, vocab, batch, context, steps, warmup, prefill_tokens, flush):
+    """Prefill ms, decode ms per step and kernel launches per decode step of one model."""
+    import torch
+
+    from . import StepEntry
+    page = 16
+    pool = batch * (context + steps + warmup + 16 + 2 * page) + prefill_tokens + 4 * page
+    llm = _engine(config_dict, page, pool, max(batch, 8), max(prefill_tokens, batch), True)
+    eng = llm.engine
+    runner, cache, sampler, kernels = eng.runner, eng.cache, eng.sampler, eng.sampler.k
+    for g in cache.groups:
+        if g.storage is not None and g.storage.dtype == torch.bfloat16:
+            g.storage.normal_(0.0, 0.5)
+    gen = torch.Generator().manual_seed(0)
+
+    def prefill():
+        cache.admit("p")
+        runner.step([StepEntry("p", toks, [prefill_tokens - 1])])
+        cache.release("p")
+    toks = torch.randint(0, vocab, (prefill_tokens,), generator=gen).tolist()
+    prefill_ms = _timed(prefill, 5, warmup, flush)
+
+    ids = [f"d{i}" for i in range(batch)]
+    for r in ids:
+        cache.admit(r)
+        cache.ensure(r, context)
+        cache.advance(r, context)
+    first = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+    prev, launches = None, 0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    prime = 5                                   # a step's shape is captured into a graph at its fourth sighting
+    for it in range(-prime, warmup + steps):
+        if it == warmup:
+            torch.cuda.synchronize()
+            launches = kernels.launches
+            start.record()
+        entries = [StepEntry(r, [t], [0]) for r, t in zip(ids, first)] if prev is None else \
+            [StepEntry(r, [0], [0], source_rows=[i]) for i, r in enumerate(ids)]
+        logits = runner.step(entries, prev_ids=prev)
+        out, _ = sampler._buffers(batch)
+        kernels.sample(logits, None, None, out)
+        prev = out
+    end.record()
+    torch.cuda.synchronize()
+    decode_ms = start.elapsed_time(end) / steps
+    launches = (kernels.launches - launches) / steps
+    kernels.check_health()
+    params = eng.runner.model.parameter_bytes()
+    del llm, eng, runner, cache
+    torch.cuda.empty_cache()
+    return {"model": name, "prefill_tokens": prefill_tokens, "prefill_ms": prefill_ms,
+            "prefill_tok_s": prefill_tokens / (prefill_ms / 1e3), "decode_batch": batch, "decode_context": context,
+            "decode_ms_per_step": decode_ms, "decode_tok_s": batch / (decode_ms / 1e3), "launches_per_decode_step": launches,
+            "parameter_bytes": params}
+
+
+def _kernels_alone(lif, llama, tokens, batch, context, hbm_gbs, flush):
+    """The family's kernels (and Llama's like ones) alone at the shapes of a `tokens`-token prompt and of a decode
+    step of `batch` requests: microseconds, bytes that must move, fraction of the copy bandwidth."""
+    import torch
+
+    from . import kernels as _k
+    K = _k.load()
+    dev, bf = "cuda", torch.bfloat16
+    att = next(l["mixer"] for l in lif["layers"] if l["type"] == "attention" and l["mixer"].get("kv_from") is None)
+    ret = next(l["mixer"] for l in lif["layers"] if l["type"] == "retention")
+    H, G, D, V, taps, chunk = att["heads"], att["kv_heads"], att["dim"], att["vdim"], att["conv"], att["mask"]["size"]
+    page = 16
+    out = []
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def record(name, us, nbytes, like=None):
+        out.append({"kernel": name, "us": round(us, 2), "mbytes": round(nbytes / 1e6, 2),
+                    "frac_of_copy_bandwidth": round(nbytes / (us * 1e-6) / (hbm_gbs * 1e9), 3), **({"like": like} if like else {})})
+
+    for label, T, B, per in (("prefill", tokens, 1, tokens), ("decode", batch, batch, 1)):
+        ctx_len = per if label == "prefill" else context
+        pages_per = -(-ctx_len // page)
+        cu, treq = [i * per for i in range(B + 1)], [b for b in range(B) for _ in range(per)]
+        pos = [ctx_len - per + i for _ in range(B) for i in range(per)]
+        table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+        slots = [int(table[b, p // page]) * page + p % page for b, p in zip(treq, pos)]
+        meta = SimpleNamespace(block_table=table, token_request=i32(treq), positions=i32(pos), query_lens=[per] * B,
+                               seq_lens_host=[ctx_len] * B, attention_plan=None)
+        # --- Lifusun: convolution + norms + cache store
+        C = H * D + G * (D + V)
+        u = torch.randn(T, C, device=dev).to(bf)
+        cache = torch.randn(B * pages_per + 1, G * page * (D + V), device=dev).to(bf)
+        q = torch.empty(T, H * D, device=dev, dtype=bf)
+        state = torch.zeros(B + 1, taps - 1, C, device=dev)
+        bias, tw = torch.randn(C, device=dev), torch.randn(C, taps, device=dev)
+        qg, kg = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
+        sl, tr, cs, ss = i32(slots), i32(treq), i32(cu), i32(list(range(B)))
+        us = 1e3 * _timed(lambda: K.conv_norm_store(u, bias, tw, qg, kg, state, ss, tr, cs, q, cache, sl, H, G, D, V, 1e-6), 10, 3, flush)
+        record(f"conv_norm_store ({label})", us, 2 * T * C * 2 + (B * (taps - 1) * C * 8 if label == "decode" else 0),
+               like="llm_rope_store")
+        # --- Llama: rotation + cache store on the same projection widths
+        if D == V:
+            qkv = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+            lcache = torch.zeros(B * pages_per + 1, 2, G, page, D, device=dev, dtype=bf)
+            inv = (1.0 / 500000.0 ** (torch.arange(0, D, 2, device=dev).float() / D)).contiguous()
+            posd = i32(pos)
+            us = 1e3 * _timed(lambda: K.rope_store(qkv, posd, inv, sl, lcache, H, G, D, D), 10, 3, flush)
+            record(f"llm_rope_store ({label})", us, T * (H + 2 * G) * D * 2 + T * (H + 2 * G) * D * 2)
+        # --- Lifusun: talking attention
+        talk = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev)).contiguous()
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+        ao = torch.empty(T, H * V, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.talking_attention(q, cache, meta, talk, slopes, ao, H, G, D, V, chunk, D ** -0.5), 10, 3, flush)
+        keys = min(chunk, ctx_len)
+        kv_read = (T if label == "decode" else -(-T // chunk)) * keys * G * (D + V) * 2
+        record(f"talking_attention ({label})", us, T * H * (D + V) * 2 + kv_read, like="llama attention")
+        # --- Llama: attention over the whole context
+        if D == V:
+            lq = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+            lo = torch.empty(T, H * D, device=dev, dtype=bf)
+            lcache.normal_(0, 0.5)
+            meta.attention_plan = None
+            us = 1e3 * _timed(lambda: K.attention(lq, lcache, meta, lo, H, G, D), 10, 3, flush)
+            rec = {"kernel": f"llama attention ({label})", "us": round(us, 2)}
+            if label == "decode":
+                nb = B * ctx_len * G * 2 * D * 2
+                rec.update(mbytes=round(nb / 1e6, 2), frac_of_copy_bandwidth=round(nb / (us * 1e-6) / (hbm_gbs * 1e9), 3))
+            else:
+                rec.update(tflops=round(4 * (T * (T + 1) // 2) * H * D / (us * 1e-6) / 1e12, 1))
+            out.append(rec)
+        # --- Lifusun: retention scan and head norm with gate
+        RH, RD, RV = ret["heads"], ret["dim"], ret["vdim"]
+        cols = 2 * RH * (RD + RV)
+        proj = torch.randn(T, cols, device=dev).to(bf)
+        half = ret["rot"]["dims"] // 2
+        ang = torch.tensor(pos, device=dev).float().unsqueeze(1) * (1.0 / 1e6 ** (torch.arange(half, device=dev).float() / half))
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        decay = torch.tensor(ret["decay"], device=dev)
+        rstate = torch.zeros(B + 1, RH, RV, RD, device=dev)
+        o = torch.empty(T, RH * RV, device=dev)
+        us = 1e3 * _timed(lambda: K.retention(proj, (cos, sin), 2 * half, decay, rstate, ss, cs, o, RH, RD, RV, RD ** -0.5, longest=per), 10, 3, flush)
+        record(f"retention_scan ({label})", us, T * RH * (2 * RD + RV) * 2 + T * RH * RV * 4 + 2 * B * RH * RD * RV * 4)
+        gated = torch.empty(T, RH * RV, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.headnorm_gate(o, proj, 2 * RH * RD + RH * RV, gated, RH, RV, 1e-6), 10, 3, flush)
+        record(f"headnorm_gate ({label})", us, T * RH * RV * (4 + 2 + 2))
+    return out
+
+
+def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_source) -> dict:
+    import torch
+
+    from .presets import SHAPES
+    peaks, source = peaks_and_source
+    if shape not in ("8b", "3b", "1b", "toy"):
+        raise SystemExit(f"--family {family}: --shape must be one of 8b, 3b, 1b, toy")
+    _, lif = SHAPES[f"{family}-{shape}"]
+    llama_name, llama = SHAPES[shape]
+    llama = dict(llama, num_hidden_layers=len(lif["layers"]))
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")       # 256 MB: larger than L2
+    t0 = time.time()
+    rows = [_model_runs(f"{family}-{shape}", lif, lif["vocab"], batch, context, steps, warmup, prefill_tokens, flush),
+            _model_runs(f"{llama_name} cut to {len(lif['layers'])} layers", llama, llama["vocab_size"], batch, context, steps, warmup,
+                        prefill_tokens, flush)]
+    alone = _kernels_alone(lif, llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
+    return {"family": family, "shape": shape, "dtype": "bf16", "data": "synthetic (random weights, random tokens)",
+            "models": rows, "kernels_alone": alone, "copy_bandwidth_gbs": peaks["hbm_gbs"], "peaks": f"of {source}",
+            "l2": "256 MB written between timed runs", "steps": steps, "warmup": warmup, "seconds": round(time.time() - t0, 1)}

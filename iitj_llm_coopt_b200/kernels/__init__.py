@@ -93,7 +93,8 @@ _SIGNATURES = {
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                               _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "llm_retention_scan": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
+                           ctypes.c_longlong, _c_void_p, _c_void_p],
     "llm_retention_headnorm_gate": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                     _c_void_p],
 }
@@ -691,17 +692,18 @@ class Kernels:
         return out
 
     def retention(self, proj, tables, rotary_dim, decay, state, state_slots, cu_seqlens, o, heads, head_dim, value_dim,
-                  k_scale, write: bool = True):
+                  k_scale, write: bool = True, longest: int = 0):
         """The retention scan (csrc/retention.cu): proj [T, >= 2*heads*head_dim + heads*value_dim] holds q, k, v of all
         heads; tables = (cos, sin) [T, rotary_dim / 2] float32 or None; decay [heads] float32; state
-        [slots, heads, head_dim, value_dim] float32 is read and, with `write`, left at the step's last token;
-        o [T, heads * value_dim] float32."""
+        [slots, heads, value_dim, head_dim] float32 (S transposed) is read and, with `write`, left at the step's last token;
+        o [T, heads * value_dim] float32.  `longest`: the most tokens one request brings, if the caller knows it (a
+        long portion is then walked in segments side by side and mended in a second pass)."""
         _check(proj, "retention.proj", tuple(DTYPE_CODE), 2)
         tokens = proj.shape[0]
         _need(proj.shape[1] >= 2 * heads * head_dim + heads * value_dim, "retention.proj: row too narrow")
         _check(decay, "retention.decay", torch.float32, 1)
         _check(state, "retention.state", torch.float32, 4)
-        _need(decay.shape[0] == heads and tuple(state.shape[1:]) == (heads, head_dim, value_dim), "retention: decay / state shapes do not fit")
+        _need(decay.shape[0] == heads and tuple(state.shape[1:]) == (heads, value_dim, head_dim), "retention: decay / state shapes do not fit")
         _check(state_slots, "retention.state_slots", torch.int32, 1)
         _check(cu_seqlens, "retention.cu_seqlens", torch.int32, 1)
         _need(cu_seqlens.shape[0] == state_slots.shape[0] + 1, "retention.cu_seqlens: requests + 1 entries")
@@ -714,9 +716,21 @@ class Kernels:
             _check(cos, "retention.cos", torch.float32, 2)
             _check(sin, "retention.sin", torch.float32, 2)
             _need(cos.shape == (tokens, half) and sin.shape == cos.shape, "retention: tables must be [tokens, rotary_dim / 2]")
-        self._call("llm_retention_scan", _ptr(proj), proj.shape[1], _ptr(cos), _ptr(sin), half, _ptr(decay), _ptr(state),
-                   _ptr(state_slots), _ptr(cu_seqlens), _ptr(o), DTYPE_CODE[proj.dtype], tokens, state_slots.shape[0], heads,
-                   head_dim, value_dim, float(k_scale), 1 if write else 0, self._stream())
+        requests = state_slots.shape[0]
+        seg, seg_floats = None, 0
+        if longest >= 256:
+            seg_floats = requests * min(32, -(-longest // 128)) * heads * value_dim * head_dim
+            if seg_floats <= (1 << 28):        # (a GiB of scratch at most; beyond that the walk stays whole)
+                seg = self._scratch("retention.segments", seg_floats, proj.device)
+        rc = self.lib.llm_retention_scan(_ptr(proj), proj.shape[1], _ptr(cos), _ptr(sin), half, _ptr(decay), _ptr(state),
+                                         _ptr(state_slots), _ptr(cu_seqlens), _ptr(o), DTYPE_CODE[proj.dtype], tokens, requests,
+                                         heads, head_dim, value_dim, float(k_scale), 1 if write else 0, int(longest), _ptr(seg),
+                                         seg_floats if seg is not None else 0,
+                                         _ptr(self._scratch("retention.rotated", tokens * heads * 2 * head_dim, proj.device)),
+                                         self._stream())
+        if rc < 0:
+            raise KernelError(f"llm_retention_scan failed ({rc}): {self.lib.llm_last_error().decode()}")
+        self.launches += 2 if rc <= 1 else 3          # rotation, walk (and its second pass)
         return o
 
     def headnorm_gate(self, o, proj, gate_col, out, heads, value_dim, eps):

@@ -3,7 +3,7 @@
     [q, k, v, g] = x W^T                     (one product; no biases)
     q, k rotated on the leading `rotary_dim` dims of each head (the mixer's position encoding; pairs (i, i + dims/2)),
     k *= head_dim^-1/2 after the rotation
-    S_t = decay_h * S_(t-1) + k_t v_t^T      per head, S [head_dim, value_dim] float32, zero for a new request
+    S_t = decay_h * S_(t-1) + k_t v_t^T      per head, S [head_dim, value_dim] float32 (kept transposed), zero for a new request
     o_t = S_t^T q_t,   each head of o divided by its root mean square,
     out = (concat_h(o) * silu(g)) W_o^T
 
@@ -45,7 +45,7 @@ class Retention(Part):
 
     @classmethod
     def cache_need(cls, spec) -> CacheNeed:
-        return CacheNeed(kind="state", state_shape=(spec.heads, spec.head_dim, spec.value_dim or spec.head_dim),
+        return CacheNeed(kind="state", state_shape=(spec.heads, spec.value_dim or spec.head_dim, spec.head_dim),
                          state_dtype="float32")
 
     def subparts(self) -> tuple:
@@ -63,7 +63,8 @@ class Retention(Part):
         tables = self.position.tables(ctx) if self.rotary_dim else None
         o = ctx.buffer("ret.o", (t, self.heads * self.value_dim), torch.float32)
         self.k.retention(proj, tables, self.rotary_dim, self.decay, state, ctx.state_slots, ctx.cu_seqlens, o,
-                         self.heads, self.head_dim, self.value_dim, self.head_dim ** -0.5, write=call.write)
+                         self.heads, self.head_dim, self.value_dim, self.head_dim ** -0.5, write=call.write,
+                         longest=max(ctx.query_lens) if ctx.query_lens else 0)
         gated = ctx.buffer("ret.gated", (t, self.heads * self.value_dim), self.dtype)
         self.k.headnorm_gate(o, proj, 2 * self.heads * self.head_dim + self.heads * self.value_dim, gated,
                              self.heads, self.value_dim, self.eps)

@@ -42,6 +42,35 @@ TINY_B = {
 TOY = dict(LLAMA_3_1_8B, hidden_size=512, intermediate_size=1408, num_hidden_layers=2, num_attention_heads=8,
            num_key_value_heads=2, head_dim=64, vocab_size=4096)
 
+
+
+def lifusun_shape(width, inner, heads, kv_heads, head_dim, vocab, blocks, chunk=64, taps=4, retention_heads=None,
+                  retention_value_dim=None) -> dict:
+    """A Lifusun config.json of `blocks` groups of four layers (retention, attention with keys and values of its own,
+    retention, attention that borrows them), with the layer sizes of a Llama of the same width: for runs with random
+    weights beside that Llama."""
+    rh = retention_heads or heads
+    rv = retention_value_dim or head_dim
+    mlp = {"kind": "dense", "ff": inner}
+    layers = []
+    for b in range(blocks):
+        ret = {"heads": rh, "dim": head_dim, "vdim": rv, "rot": {"dims": head_dim, "base": 1000000.0},
+               "decay": [1.0 - 2.0 ** (-5 - 7 * h / max(rh - 1, 1)) for h in range(rh)]}
+        att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+               "conv": taps, "mask": {"size": chunk}}
+        layers += [{"type": "retention", "mixer": dict(ret), "mlp": dict(mlp)},
+                   {"type": "attention", "mixer": dict(att), "mlp": dict(mlp)},
+                   {"type": "retention", "mixer": dict(ret), "mlp": dict(mlp)},
+                   {"type": "attention", "mixer": dict(att, kv_from=4 * b + 1), "mlp": dict(mlp)}]
+    return {"architecture": "Lifusun", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+# Lifusun at the layer sizes of the Llama shapes above (8 layers each; a Llama cut to 8 layers stands beside them)
+LIFUSUN_8B = lifusun_shape(4096, 14336, 32, 8, 128, 128256, blocks=2)
+LIFUSUN_3B = lifusun_shape(3072, 8192, 24, 8, 128, 128256, blocks=2)
+LIFUSUN_1B = lifusun_shape(2048, 8192, 32, 8, 64, 128256, blocks=2)
+LIFUSUN_TOY = lifusun_shape(512, 1408, 8, 2, 64, 4096, blocks=1)
+
 # name -> (label used in reports, config.json dict)
 SHAPES = {
     "8b": ("llama-3.1-8b-shape-random", LLAMA_3_1_8B),
@@ -50,6 +79,10 @@ SHAPES = {
     "tinyA": ("llama-tiny-a-shape-random", TINY_A),
     "tinyB": ("llama-tiny-b-shape-random", TINY_B),
     "toy": ("llama-toy-shape-random", TOY),
+    "lifusun-8b": ("lifusun-8b-layers-random", LIFUSUN_8B),
+    "lifusun-3b": ("lifusun-3b-layers-random", LIFUSUN_3B),
+    "lifusun-1b": ("lifusun-1b-layers-random", LIFUSUN_1B),
+    "lifusun-toy": ("lifusun-toy-layers-random", LIFUSUN_TOY),
 }
 
 

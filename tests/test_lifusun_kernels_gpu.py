@@ -139,12 +139,12 @@ def test_talking_attention_edges_of_a_chunk(K, dtype):
     others = torch.ones(n, dtype=torch.bool, device=DEV)
     others[[chunk - 1, 2 * chunk - 1]] = False           # (the planted key's own position sees it: the last key of its own chunk)
     assert out[others].float().abs().max() < 100         # no query of the next chunk saw the key just outside
-    assert (out[chunk:2 * chunk].float().min(dim=1).values < -0.05).all()     # every query of the chunk saw its first key
+    assert (out[chunk:2 * chunk - 1].float().min(dim=1).values < -0.05).all()     # every query of the chunk saw its first key
     close(out, want, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim,vdim,rot", [(2, 32, 32, 32), (1, 20, 12, 10), (3, 24, 40, 24), (4, 8, 16, 0), (2, 64, 128, 32), (2, 160, 40, 64)])
+@pytest.mark.parametrize("heads,dim,vdim,rot", [(2, 32, 32, 32), (1, 20, 12, 10), (3, 24, 40, 24), (4, 8, 16, 0), (2, 64, 128, 32), (2, 160, 40, 64), (40, 32, 128, 32), (80, 32, 128, 0)])
 def test_retention_scan(K, dtype, heads, dim, vdim, rot):
     torch.manual_seed(dim)
     lens = [37, 1, 2, 18]
@@ -157,8 +157,8 @@ def test_retention_scan(K, dtype, heads, dim, vdim, rot):
     if half:
         ang = pos.float().unsqueeze(1) * (1.0 / (10000.0 ** (torch.arange(half, device=DEV).float() / half)))
         cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
-    decay = torch.tensor([0.9, 0.99, 0.999, 0.5][:heads], device=DEV)
-    state = torch.randn(6, heads, dim, vdim, device=DEV)
+    decay = torch.tensor(([0.9, 0.99, 0.999, 0.5] * 20)[:heads], device=DEV)
+    state = torch.randn(6, heads, vdim, dim, device=DEV)
     state[2].zero_()
     slots, cu = [4, 2, 0, 5], [0, 37, 38, 40, 58]
     want, new = R.ref_retention(proj, cos, sin, rot, decay, state, slots, cu, heads, dim, vdim, dim ** -0.5)
@@ -174,6 +174,35 @@ def test_retention_scan(K, dtype, heads, dim, vdim, rot):
     assert torch.equal(st2, state)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dim,vdim,rot,lens", [(3, 32, 16, 16, [700, 300, 5, 129]), (2, 64, 64, 64, [257]), (1, 20, 12, 10, [1000, 1]),
+                                                     (16, 64, 64, 64, [4100])])
+def test_retention_long_portions_in_segments(K, dtype, heads, dim, vdim, rot, lens):
+    """Portions long enough to be walked in segments side by side and mended in a second pass, beside short ones that
+    are not; states that are not zero at the start; the state afterwards."""
+    torch.manual_seed(sum(lens))
+    T, B = sum(lens), len(lens)
+    proj = (torch.randn(T, 2 * heads * (dim + vdim), device=DEV) * 0.5).to(dtype)
+    half = rot // 2
+    pos = torch.cat([torch.arange(50 * b, 50 * b + n) for b, n in enumerate(lens)]).to(DEV)
+    ang = pos.float().unsqueeze(1) * (1.0 / (10000.0 ** (torch.arange(half, device=DEV).float() / half)))
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    decay = torch.tensor(([0.9, 0.99, 0.999, 0.9995] * 4)[:heads], device=DEV)
+    state = torch.randn(B + 2, heads, vdim, dim, device=DEV)
+    slots = list(range(B, 0, -1))
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    want, new = R.ref_retention(proj, cos, sin, rot, decay, state, slots, cu, heads, dim, vdim, dim ** -0.5)
+    st = state.clone()
+    o = torch.empty(T, heads * vdim, device=DEV)
+    K.retention(proj, (cos, sin), rot, decay, st, i32(slots), i32(cu), o, heads, dim, vdim, dim ** -0.5, write=True, longest=max(lens))
+    close(o, want, torch.float32, "o")
+    for slot, S in new.items():
+        close(st[slot], S, torch.float32, "state")
+    assert torch.equal(st[0], state[0]) and torch.equal(st[B + 1], state[B + 1])
+
+
 def test_retention_keeps_a_far_key(K):
     """600 tokens; only the first one has a key that the last query lines up with, and a value nothing else has: what the
     last token reads is that value, decayed 599 times."""
@@ -185,12 +214,13 @@ def test_retention_keeps_a_far_key(K):
     proj[0, 2 * dim:2 * dim + vdim] = torch.arange(1, vdim + 1, device=DEV).float()
     proj[T - 1, :dim] = 1.0
     decay = torch.tensor([1 - 2.0 ** -11], device=DEV)
-    state = torch.zeros(2, heads, dim, vdim, device=DEV)
+    state = torch.zeros(2, heads, vdim, dim, device=DEV)
     o = torch.empty(T, vdim, device=DEV)
     want, _ = R.ref_retention(proj, None, None, 0, decay, state, [1], [0, T], heads, dim, vdim, 0.25)
     # in three portions, the state carried in between
     for lo, hi in ((0, 1), (1, 333), (333, T)):
-        K.retention(proj[lo:hi].contiguous(), None, 0, decay, state, i32([1]), i32([0, hi - lo]), o[lo:hi], heads, dim, vdim, 0.25)
+        K.retention(proj[lo:hi].contiguous(), None, 0, decay, state, i32([1]), i32([0, hi - lo]), o[lo:hi], heads, dim, vdim, 0.25,
+                    longest=hi - lo)         # (the portions of 332 and 267 tokens are walked in segments)
     expect = 4.0 * 0.25 * dim * float(decay) ** (T - 1) * torch.arange(1, vdim + 1).float()
     assert (o[T - 1].cpu() - expect).abs().max() < 0.05 * expect.max()
     close(o, want, torch.float32)

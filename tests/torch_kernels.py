@@ -149,7 +149,7 @@ def ref_talking_attention(q, cache, block_table, token_request, positions, talk,
 
 
 def ref_retention(proj, cos, sin, rotary_dim, decay, state, state_slots, cu_seqlens, heads, head_dim, value_dim, k_scale):
-    """proj [T, q | k | v | ...]; state [slots, H, D, V] float32 (read, and returned updated as {slot: [H, D, V]});
+    """proj [T, q | k | v | ...]; state [slots, H, V, D] float32, S transposed (read, and returned updated as {slot: [H, V, D]});
     returns (o [T, H*V] float32, new states)."""
     T = proj.shape[0]
     qk = heads * head_dim
@@ -170,11 +170,11 @@ def ref_retention(proj, cos, sin, rotary_dim, decay, state, state_slots, cu_seql
     d = decay.float().view(heads, 1, 1)
     for b in range(len(cu) - 1):
         slot = int(state_slots[b])
-        S = state[slot].float().clone()
+        S = state[slot].float().transpose(-1, -2).clone()
         for t in range(cu[b], cu[b + 1]):
             S = d * S + k[t].unsqueeze(-1) * v[t].unsqueeze(-2)
             o[t] = torch.einsum("hdv,hd->hv", S, q[t])
-        new[slot] = S
+        new[slot] = S.transpose(-1, -2).contiguous()
     return o.view(T, heads * value_dim), new
 
 
@@ -285,7 +285,7 @@ class TorchKernels:
         return out
 
     def retention(self, proj, tables, rotary_dim, decay, state, state_slots, cu_seqlens, o, heads, head_dim, value_dim,
-                  k_scale, write=True):
+                  k_scale, write=True, longest=0):
         cos, sin = tables if tables is not None else (None, None)
         got, new = ref_retention(proj, cos, sin, rotary_dim, decay, state, state_slots, cu_seqlens, heads, head_dim,
                                  value_dim, k_scale)
