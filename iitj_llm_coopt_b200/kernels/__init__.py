@@ -94,7 +94,7 @@ _SIGNATURES = {
                               _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "llm_retention_scan": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
-                           ctypes.c_longlong, _c_void_p, _c_void_p],
+                           ctypes.c_longlong, _c_void_p, _c_int, _c_int, _c_void_p],
     "llm_retention_headnorm_gate": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                     _c_void_p],
 }
@@ -300,6 +300,8 @@ class Kernels:
         self.decode_tma = os.environ.get("IITJ_DECODE_TMA", "1") != "0"     # decode attention fetches keys and values by TMA
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
+        self.retention_blocks = int(os.environ.get("IITJ_RETENTION_BLOCKS", "0"))        # blocks the retention walk aims at (0: its own rule)
+        self.retention_segments = int(os.environ.get("IITJ_RETENTION_SEGMENTS", "0"))    # 1: never in segments, 2: always
         if os.environ.get("IITJ_PDL", "1") == "0":
             self.lib.llm_set_pdl(0)
         self._scratch_bufs: dict = {}
@@ -727,7 +729,7 @@ class Kernels:
                                          heads, head_dim, value_dim, float(k_scale), 1 if write else 0, int(longest), _ptr(seg),
                                          seg_floats if seg is not None else 0,
                                          _ptr(self._scratch("retention.rotated", tokens * heads * 2 * head_dim, proj.device)),
-                                         self._stream())
+                                         self.retention_blocks, self.retention_segments, self._stream())
         if rc < 0:
             raise KernelError(f"llm_retention_scan failed ({rc}): {self.lib.llm_last_error().decode()}")
         self.launches += 2 if rc <= 1 else 3          # rotation, walk (and its second pass)
