@@ -5,8 +5,8 @@
 //     p[h, :] = softmax_j a[h, :],     out[h] = sum_j p[h, j] v[kv(h), j]
 // A query sees the keys j <= i of its request; with chunk > 0 only those of its own chunk (j / chunk == i / chunk,
 // counted from the request's position 0).  Because every head's score of a key enters every head's softmax,
-// one block works on all heads of a token: the scores of a tile of 32 keys land in shared memory, are mixed there,
-// and then each warp runs the running softmax and the value sum of its heads.
+// one block works on all heads of a token: the scores of a tile of 32 keys land in shared memory, each warp mixes them
+// for its own heads (a lane per key) and then runs the running softmax and the value sum of those heads.
 //
 // Key tiles start at multiples of 32 of the key position and sums run in a fixed order, so a position's result
 // does not depend on how the request was cut into steps or on what else is in the batch.
@@ -29,10 +29,11 @@ __device__ __forceinline__ float dot_any<float>(const float* __restrict__ k, con
     if (vec) {
         for (int i = 0; i < d; i += 4) {
             const float4 kv = *reinterpret_cast<const float4*>(k + i);
-            acc = fmaf(kv.x, q[i], acc);
-            acc = fmaf(kv.y, q[i + 1], acc);
-            acc = fmaf(kv.z, q[i + 2], acc);
-            acc = fmaf(kv.w, q[i + 3], acc);
+            const float4 qv = *reinterpret_cast<const float4*>(q + i);
+            acc = fmaf(kv.x, qv.x, acc);
+            acc = fmaf(kv.y, qv.y, acc);
+            acc = fmaf(kv.z, qv.z, acc);
+            acc = fmaf(kv.w, qv.w, acc);
         }
     } else {
         for (int i = 0; i < d; ++i) acc = fmaf(k[i], q[i], acc);
@@ -48,17 +49,28 @@ __device__ __forceinline__ float dot_any<__nv_bfloat16>(const __nv_bfloat16* __r
         for (int i = 0; i < d; i += 8) {
             const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
             const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float4 qa = *reinterpret_cast<const float4*>(q + i), qb = *reinterpret_cast<const float4*>(q + i + 4);
+            const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __bfloat1622float2(p[j]);
-                acc = fmaf(f.x, q[i + 2 * j], acc);
-                acc = fmaf(f.y, q[i + 2 * j + 1], acc);
+                acc = fmaf(f.x, qv[2 * j], acc);
+                acc = fmaf(f.y, qv[2 * j + 1], acc);
             }
         }
     } else {
         for (int i = 0; i < d; ++i) acc = fmaf(__bfloat162float(k[i]), q[i], acc);
     }
     return acc;
+}
+
+__device__ __forceinline__ float2 pair_f32(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 pair_f32(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
 template <typename T, int HPW>
@@ -71,10 +83,10 @@ __global__ void talking_attn_kernel(const T* __restrict__ q, int q_stride, const
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
+    const int hp = (heads + 7) & ~7;            // a row of the mixing matrix in shared memory, padded to 32 bytes
     float* qs = smem;                           // [heads, dim]
-    float* talk_s = qs + heads * dim;           // [heads, heads]
-    float* S = talk_s + heads * heads;          // [heads, kTile] scores before mixing
-    float* A = S + heads * kTile;               // [heads, kTile] after mixing
+    float* talk_s = qs + ((heads * dim + 3) & ~3);   // [heads (g), hp (h)]: transposed, so that a warp's heads lie side by side
+    float* S = talk_s + heads * hp;             // [heads, kTile] scores before mixing
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[t];
@@ -83,7 +95,10 @@ __global__ void talking_attn_kernel(const T* __restrict__ q, int q_stride, const
     const int group = heads / kv_heads;
 
     for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) qs[i] = to_f32(q[(size_t)t * q_stride + i]);
-    for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) talk_s[i] = talk[i];
+    for (int i = threadIdx.x; i < heads * hp; i += blockDim.x) {
+        const int g = i / hp, h = i % hp;
+        talk_s[i] = h < heads ? talk[h * heads + g] : 0.f;
+    }
 
     constexpr int kOwn = kMaxValueDim / 32;
     float acc[HPW][kOwn], m[HPW], l[HPW];
@@ -115,17 +130,34 @@ __global__ void talking_attn_kernel(const T* __restrict__ q, int q_stride, const
             S[g * kTile + lane] = s;
         }
         __syncthreads();
-        for (int h = warp; h < heads; h += (blockDim.x >> 5)) {
-            float a = 0.f;
-            for (int g = 0; g < heads; ++g) a = fmaf(talk_s[h * heads + g], S[g * kTile + lane], a);
-            A[h * kTile + lane] = valid ? a : -INFINITY;
+        // the warp's own heads after mixing: a[i] = sum_g talk[h_i, g] * s[g, this lane's key], g ascending
+        float a[HPW];
+#pragma unroll
+        for (int i = 0; i < HPW; ++i) a[i] = 0.f;
+        {
+            const float* trow = talk_s + warp * HPW;
+            for (int g = 0; g < heads; ++g, trow += hp) {
+                const float sg = S[g * kTile + lane];
+                if (HPW % 4 == 0) {
+#pragma unroll
+                    for (int i = 0; i < HPW; i += 4) {
+                        const float4 w = *reinterpret_cast<const float4*>(trow + i);
+                        a[i] = fmaf(w.x, sg, a[i]);
+                        a[i + 1] = fmaf(w.y, sg, a[i + 1]);
+                        a[i + 2] = fmaf(w.z, sg, a[i + 2]);
+                        a[i + 3] = fmaf(w.w, sg, a[i + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < HPW; ++i) a[i] = fmaf(trow[i], sg, a[i]);
+                }
+            }
         }
-        __syncthreads();
 #pragma unroll
         for (int i = 0; i < HPW; ++i) {
             const int h = warp * HPW + i;
             if (h >= heads) break;                       // the whole warp leaves together
-            const float s = A[h * kTile + lane];
+            const float s = valid ? a[i] : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));   // finite: every tile holds a visible key
             const float corr = expf(m[i] - m_new);          // 0 on the first tile
             const float p = valid ? expf(s - m_new) : 0.f;
@@ -144,15 +176,33 @@ __global__ void talking_attn_kernel(const T* __restrict__ q, int q_stride, const
                     v[u] = cache + __shfl_sync(0xffffffffu, vo, j0 + u);
                 }
                 if (pj[0] + pj[1] + pj[2] + pj[3] + pj[4] + pj[5] + pj[6] + pj[7] == 0.f) continue;   // same for the whole warp
+                if (vec) {
+                    // a lane owns the dims 2 * lane, 2 * lane + 1 (+ 64, + 128, ...): one load for two of them
 #pragma unroll
-                for (int r = 0; r < kOwn; ++r) {
-                    const int d = lane + 32 * r;
-                    if (d < vdim) {
-                        float x[8];
+                    for (int r = 0; r < kOwn; r += 2) {
+                        const int d = 2 * lane + 32 * r;
+                        if (d < vdim) {
+                            float2 x[8];
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) x[u] = pj[u] != 0.f ? to_f32(v[u][d]) : 0.f;
+                            for (int u = 0; u < 8; ++u) x[u] = pj[u] != 0.f ? pair_f32(v[u] + d) : make_float2(0.f, 0.f);
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) acc[i][r] = fmaf(pj[u], x[u], acc[i][r]);
+                            for (int u = 0; u < 8; ++u) {
+                                acc[i][r] = fmaf(pj[u], x[u].x, acc[i][r]);
+                                acc[i][r + 1] = fmaf(pj[u], x[u].y, acc[i][r + 1]);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < kOwn; ++r) {
+                        const int d = lane + 32 * r;
+                        if (d < vdim) {
+                            float x[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) x[u] = pj[u] != 0.f ? to_f32(v[u][d]) : 0.f;
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) acc[i][r] = fmaf(pj[u], x[u], acc[i][r]);
+                        }
                     }
                 }
             }
@@ -165,10 +215,18 @@ __global__ void talking_attn_kernel(const T* __restrict__ q, int q_stride, const
         if (h >= heads) break;
         const float inv = 1.0f / l[i];
         T* orow = out + (size_t)t * out_stride + (size_t)h * vdim;
+        if (vec) {
 #pragma unroll
-        for (int r = 0; r < kOwn; ++r) {
-            const int d = lane + 32 * r;
-            if (d < vdim) orow[d] = from_f32<T>(acc[i][r] * inv);
+            for (int r = 0; r < kOwn; r += 2) {
+                const int d = 2 * lane + 32 * r;
+                if (d < vdim) store_pair(orow + d, acc[i][r] * inv, acc[i][r + 1] * inv);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < kOwn; ++r) {
+                const int d = lane + 32 * r;
+                if (d < vdim) orow[d] = from_f32<T>(acc[i][r] * inv);
+            }
         }
     }
 }
@@ -179,7 +237,7 @@ int launch_talking(const void* q, int q_stride, const void* cache, long long pag
                    const float* talk, const float* slopes, void* out, int out_stride, int tokens, int heads, int kv_heads,
                    int dim, int vdim, int page_size, int chunk, float scale, int vec, cudaStream_t stream) {
     const int warps = (heads + HPW - 1) / HPW;
-    const size_t smem = sizeof(float) * ((size_t)heads * dim + (size_t)heads * heads + 2 * (size_t)heads * kTile);
+    const size_t smem = sizeof(float) * ((((size_t)heads * dim + 3) & ~(size_t)3) + (size_t)heads * ((heads + 7) & ~7) + (size_t)heads * kTile);
     if (smem > 200 * 1024) LLM_FAIL(-1, "talking attention: %d heads of %d dims do not fit shared memory", heads, dim);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(talking_attn_kernel<T, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
