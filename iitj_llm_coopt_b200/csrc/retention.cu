@@ -341,9 +341,11 @@ retention_tile_kernel(const T* __restrict__ proj, int proj_stride, const float* 
         if (t0 + tb < end)
             stage_rows<T>(stage_q(stage ^ 1), stage_q(stage ^ 1) + tb * dim, stage_v(stage ^ 1), qk, proj, proj_stride, heads, h, t0 + tb,
                           min(tb, end - t0 - tb), dim, cpb, v_col, vcols, true, vvec);
-        for (int idx = threadIdx.x; idx < nb * cpb; idx += blockDim.x)
-            vs[idx] = (idx % cpb) < vcols ? to_f32(rawv[idx]) : 0.f;
-        __syncthreads();
+        if (MODE == 0) {
+            for (int idx = threadIdx.x; idx < nb * cpb; idx += blockDim.x)
+                vs[idx] = (idx % cpb) < vcols ? to_f32(rawv[idx]) : 0.f;
+            __syncthreads();
+        }
         for (int tt = 0; tt < nb; ++tt) {
             float part[4] = {0.f, 0.f, 0.f, 0.f};
             float v4[4];
@@ -385,7 +387,7 @@ retention_tile_kernel(const T* __restrict__ proj, int proj_stride, const float* 
                 for (int o = 4; o < ds; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
                 if (live && s < 4) {
                     if (MODE == 0) o_at[col_of_lane] = sum;
-                    else o_at[col_of_lane] += carried * sum;
+                    else vs[tt * cpb + 4 * cg + col_of_lane] = carried * sum;      // (the second pass has no use for values: vs collects what it adds)
                 }
             } else {
 #pragma unroll
@@ -395,9 +397,17 @@ retention_tile_kernel(const T* __restrict__ proj, int proj_stride, const float* 
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (MODE == 0) o_at[j] = part[j];
-                        else o_at[j] += carried * part[j];
+                        else vs[tt * cpb + 4 * cg + j] = carried * part[j];
                     }
                 }
+            }
+        }
+        if (MODE == 1) {
+            // what this block of tokens is to be given, added with all loads in flight at once
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < nb * cpb; idx += blockDim.x) {
+                const int tt = idx / cpb, x = idx % cpb;
+                if (x < vcols) out[(size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c0 + x] += vs[idx];
             }
         }
     }

@@ -26,9 +26,10 @@ __device__ __forceinline__ void load2(const __nv_bfloat16* p, float& a, float& b
     b = v.y;
 }
 
-template <typename T>
+// TAPS > 0: the number of taps is known when compiling (the loops over taps unroll to exactly that many); 0: any number.
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(256)
-conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, const float* __restrict__ taps_w, int taps,
+conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, const float* __restrict__ taps_w, int taps_any,
                        const float* __restrict__ q_gain, const float* __restrict__ k_gain,
                        const float* __restrict__ state, const int* __restrict__ state_slots,
                        const int* __restrict__ token_request, const int* __restrict__ cu_seqlens,
@@ -39,6 +40,8 @@ conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, 
     pdl_wait();
     extern __shared__ float y[];  // channels floats
     __shared__ float red[32];
+    const int taps = TAPS > 0 ? TAPS : taps_any;
+    constexpr int kUnroll = TAPS > 0 ? TAPS : kMaxTaps;
     const int t = blockIdx.x;
     const int b = token_request[t];
     const int local = t - cu_seqlens[b];
@@ -50,9 +53,9 @@ conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, 
         // two neighbouring channels per thread and load; the taps' loads of a pair are all asked for before the first is used
         for (int c = 2 * threadIdx.x; c < channels; c += 2 * blockDim.x) {
             const float b0 = bias ? bias[c] : 0.f, b1 = bias ? bias[c + 1] : 0.f;
-            float x0[kMaxTaps], x1[kMaxTaps];
+            float x0[kUnroll], x1[kUnroll];
 #pragma unroll
-            for (int j = 0; j < kMaxTaps; ++j) {
+            for (int j = 0; j < kUnroll; ++j) {
                 if (j < taps) {
                     const int src = local - (back - j);
                     if (src >= 0) {
@@ -69,7 +72,7 @@ conv_norm_store_kernel(const T* __restrict__ u, const float* __restrict__ bias, 
             float a0 = 0.f, a1 = 0.f;
             if (taps_w) {
 #pragma unroll
-                for (int j = 0; j < kMaxTaps; ++j) {
+                for (int j = 0; j < kUnroll; ++j) {
                     if (j < taps) {
                         a0 = fmaf(taps_w[(size_t)c * taps + j], x0[j], a0);
                         a1 = fmaf(taps_w[(size_t)(c + 1) * taps + j], x1[j], a1);
@@ -179,11 +182,22 @@ LLM_API int llm_conv_norm_store(const void* u, const float* bias, const float* t
     if (smem > 200 * 1024) LLM_FAIL(-1, "short convolution: %d channels do not fit shared memory", channels);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(conv_norm_store_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llm_launch(conv_norm_store_kernel<T>, tokens, 256, smem, stream, (const T*)u, bias, taps_w, taps, q_gain, k_gain,
-                   (const float*)state, state_slots, token_request, cu_seqlens, (T*)q_out, (T*)cache, slots, page_stride,
-                   page_size, heads, kv_heads, dim, vdim, channels, eps);
+#define LLM_CONV(TT)                                                                                                       \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024)                                                                                              \
+            cudaFuncSetAttribute(conv_norm_store_kernel<T, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        llm_launch(conv_norm_store_kernel<T, TT>, tokens, 256, smem, stream, (const T*)u, bias, taps_w, taps, q_gain, k_gain, \
+                   (const float*)state, state_slots, token_request, cu_seqlens, (T*)q_out, (T*)cache, slots, page_stride,   \
+                   page_size, heads, kv_heads, dim, vdim, channels, eps);                                                   \
+    } while (0)
+        switch (taps) {           // the usual sizes unrolled, the rest by the general form
+            case 1: LLM_CONV(1); break;
+            case 2: LLM_CONV(2); break;
+            case 3: LLM_CONV(3); break;
+            case 4: LLM_CONV(4); break;
+            default: LLM_CONV(0); break;
+        }
+#undef LLM_CONV
         LLM_CHECK_LAUNCH("conv_norm_store");
         if (taps > 1) {
             const int by = (channels + 255) / 256 < 8 ? (channels + 255) / 256 : 8;
