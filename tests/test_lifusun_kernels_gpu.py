@@ -95,7 +95,7 @@ def paged_case(dtype, heads, kv_heads, dim, vdim, page, seqs, seed=0):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,page,chunk", [(4, 2, 16, 24, 16, 16), (6, 6, 32, 32, 8, 32), (1, 1, 12, 20, 4, 128),
-                                                                (20, 5, 8, 16, 4, 8), (8, 8, 96, 96, 16, 64), (40, 8, 64, 128, 16, 0),
+                                                                (20, 5, 8, 16, 4, 8), (8, 4, 96, 80, 16, 48), (40, 8, 64, 128, 16, 0),
                                                                 (3, 3, 40, 8, 32, 48)])
 def test_talking_attention(K, dtype, heads, kv_heads, dim, vdim, page, chunk):
     # prompt portions that start and end inside chunks and pages beside single decoded tokens at, before and after edges
@@ -144,7 +144,7 @@ def test_talking_attention_edges_of_a_chunk(K, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim,vdim,rot", [(2, 32, 32, 32), (1, 20, 12, 10), (3, 24, 40, 24), (4, 8, 16, 0), (2, 64, 128, 32), (2, 160, 40, 64), (40, 32, 128, 32), (80, 32, 128, 0)])
+@pytest.mark.parametrize("heads,dim,vdim,rot", [(2, 32, 48, 32), (1, 20, 12, 10), (3, 24, 40, 24), (4, 8, 16, 0), (2, 64, 128, 32), (2, 160, 40, 64), (40, 32, 128, 32), (80, 32, 128, 0)])
 def test_retention_scan(K, dtype, heads, dim, vdim, rot):
     torch.manual_seed(dim)
     lens = [37, 1, 2, 18]
