@@ -94,7 +94,10 @@ def make_tensors(cfg, seed, std=0.08):
             t[p + "talk"] = torch.eye(m["heads"]) + normal(m["heads"], m["heads"], s=0.3)
             t[p + "o"] = normal(w, m["heads"] * m["vdim"])
         else:
-            t[p + "q"], t[p + "k"] = normal(m["heads"] * m["dim"], w), normal(m["heads"] * m["dim"], w)
+            # k leans towards q: a request's first token reads sign(q . k) * v / |v| from a retention layer, which no
+            # number format gets right when q . k happens to be next to nothing
+            t[p + "q"] = normal(m["heads"] * m["dim"], w)
+            t[p + "k"] = t[p + "q"] + 0.6 * normal(m["heads"] * m["dim"], w)
             t[p + "v"], t[p + "g"] = normal(m["heads"] * m["vdim"], w), normal(m["heads"] * m["vdim"], w)
             t[p + "o"] = normal(w, m["heads"] * m["vdim"])
         if lay["mlp"] is not None:
