@@ -150,10 +150,14 @@ def _kernels_alone(lif, llama, tokens, batch, context, hbm_gbs, flush):
         talk = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev)).contiguous()
         slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
         ao = torch.empty(T, H * V, device=dev, dtype=bf)
-        us = 1e3 * _timed(lambda: K.talking_attention(q, cache, meta, talk, slopes, ao, H, G, D, V, chunk, D ** -0.5), 10, 3, flush)
         keys = min(chunk, ctx_len)
         kv_read = (T if label == "decode" else -(-T // chunk)) * keys * G * (D + V) * 2
-        record(f"talking_attention ({label})", us, T * H * (D + V) * 2 + kv_read, like="llama attention")
+        us = 1e3 * _timed(lambda: K.talking_attention(q, cache, meta, talk, slopes, ao, H, G, D, V, chunk, D ** -0.5), 10, 3, flush)
+        record(f"talking_attention, a token a block ({label})", us, T * H * (D + V) * 2 + kv_read, like="llama attention")
+        if label == "prefill":
+            tiles = i32([[r, min(16, T - r), pos[r], treq[r]] for r in range(0, T, 16)])
+            us = 1e3 * _timed(lambda: K.talking_attention(q, cache, meta, talk, slopes, ao, H, G, D, V, chunk, D ** -0.5, tiles=tiles), 10, 3, flush)
+            record(f"talking_attention, 16 tokens a block on the tensor core ({label})", us, T * H * (D + V) * 2 + kv_read, like="llama attention")
         # --- Llama: attention over the whole context
         if D == V:
             lq = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)

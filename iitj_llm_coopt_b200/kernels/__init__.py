@@ -92,6 +92,10 @@ _SIGNATURES = {
     "llm_talking_attention": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                               _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_talking_attention_mma_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_longlong],
+    "llm_talking_attention_mma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
+                                  _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                  _c_float, _c_void_p],
     "llm_retention_scan": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
                            ctypes.c_longlong, _c_void_p, _c_int, _c_int, _c_void_p],
@@ -300,6 +304,7 @@ class Kernels:
         self.decode_tma = os.environ.get("IITJ_DECODE_TMA", "1") != "0"     # decode attention fetches keys and values by TMA
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
+        self.talking_mma = os.environ.get("IITJ_TALKING_MMA", "1") != "0"               # tensor-core talking attention for prompt portions
         self.retention_blocks = int(os.environ.get("IITJ_RETENTION_BLOCKS", "0"))        # blocks the retention walk aims at (0: its own rule)
         self.retention_segments = int(os.environ.get("IITJ_RETENTION_SEGMENTS", "0"))    # 1: never in segments, 2: always
         if os.environ.get("IITJ_PDL", "1") == "0":
@@ -670,9 +675,12 @@ class Kernels:
             self.launches += 1      # the state's own kernel
         return q_out
 
-    def talking_attention(self, q, cache_layer, meta, talk, slopes, out, heads, kv_heads, head_dim, value_dim, chunk, scale):
+    def talking_attention(self, q, cache_layer, meta, talk, slopes, out, heads, kv_heads, head_dim, value_dim, chunk, scale,
+                          tiles=None):
         """Attention with a distance bias (slopes [heads]) and heads mixed before the softmax (talk [heads, heads]),
-        over the keys of the query's own chunk (`chunk` 0: all earlier keys); csrc/talking_attention.cu."""
+        over the keys of the query's own chunk (`chunk` 0: all earlier keys); csrc/talking_attention.cu.  `tiles`
+        [n, 4] int32 (first token row, rows up to 16, position of the first row, request) cuts the step's tokens into
+        runs of one request: with them, bfloat16 and sizes it takes, the tensor-core form runs (csrc/talking_attention_mma.cu)."""
         _check(q, "talking_attention.q", tuple(DTYPE_CODE), 2)
         _check(cache_layer, "talking_attention.cache", q.dtype, 2)
         _check(out, "talking_attention.out", q.dtype, 2)
@@ -687,6 +695,15 @@ class Kernels:
         _need(meta.token_request.shape[0] == tokens and meta.positions.shape[0] == tokens,
               "talking_attention: one token_request and one position per token")
         page_size = self._page_size_of(cache_layer, kv_heads, head_dim, value_dim)
+        if tiles is not None and q.dtype == torch.bfloat16 and self.talking_mma and \
+                self.lib.llm_talking_attention_mma_supported(heads, kv_heads, head_dim, value_dim, int(chunk), cache_layer.shape[1]):
+            _check(tiles, "talking_attention.tiles", torch.int32, 2)
+            _need(tiles.shape[1] == 4, "talking_attention.tiles: [n, 4]")
+            self._call("llm_talking_attention_mma", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1],
+                       kv_heads * page_size * head_dim, _ptr(meta.block_table), meta.block_table.shape[1], _ptr(tiles),
+                       tiles.shape[0], _ptr(talk), _ptr(slopes), _ptr(out), out.shape[1], heads, kv_heads, head_dim, value_dim,
+                       page_size, int(chunk), float(scale), self._stream())
+            return out
         self._call("llm_talking_attention", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1],
                    kv_heads * page_size * head_dim, _ptr(meta.block_table), meta.block_table.shape[1], _ptr(meta.token_request),
                    _ptr(meta.positions), _ptr(talk), _ptr(slopes), _ptr(out), out.shape[1], DTYPE_CODE[q.dtype], tokens,

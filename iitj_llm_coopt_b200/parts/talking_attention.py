@@ -24,11 +24,13 @@ from __future__ import annotations
 import torch
 
 from ..config.specs import CacheNeed
-from .base import ParamSpec, Part
+from .base import ParamSpec, Part, StepPlan
 
 
 class TalkingAttention(Part):
     graph_safe = True
+    prepare_key = "talking_attention"      # every such layer of a model shares one plan of the step's query tiles
+    TILE = 16                              # query tokens of one request a block of the tensor-core kernel takes
 
     def __init__(self, spec, kernels, dtype, position=None):
         self.spec, self.k, self.dtype = spec, kernels, dtype
@@ -83,6 +85,19 @@ class TalkingAttention(Part):
         return CacheNeed(kind="state", state_shape=(max(int(spec.option("conv_taps", 0)) - 1, 0), cls._channels(spec)),
                          state_dtype="float32")
 
+    def prepare_step(self, shape):
+        """A step with prompt portions: its tokens cut into runs of up to TILE tokens of one request (first token row,
+        rows, position of the first row, request), for the kernel that takes a tile of queries at a time.  A step of
+        single decoded tokens needs none (the one-token kernel runs)."""
+        if shape.decode_shaped or shape.num_tokens == len(shape.query_lens):
+            return None
+        tiles, row = [], 0
+        for b, (n, total) in enumerate(zip(shape.query_lens, shape.seq_lens)):
+            for s in range(0, n, self.TILE):
+                tiles += [row + s, min(self.TILE, n - s), total - n + s, b]
+            row += n
+        return StepPlan(arrays={"tiles": tiles})
+
     def load(self, tensors: dict) -> None:
         for name, t in tensors.items():        # the small tensors enter float32 arithmetic: kept in float32
             setattr(self, name, t if name in ("qkv", "o") else t.float().contiguous())
@@ -107,7 +122,9 @@ class TalkingAttention(Part):
                                meta.slots if self.own_kv else None, self.heads, self.kv_heads, self.head_dim,
                                self.value_dim, self.eps)
         attn = ctx.buffer("tattn.ctx", (t, self.heads * self.value_dim), self.dtype)
+        plan = ctx.prepared.get(self.prepare_key)
+        tiles = plan.device_arrays.get("tiles") if plan is not None else None
         self.k.talking_attention(q, view, meta, self.talk, self.slopes, attn, self.heads, self.kv_heads, self.head_dim,
-                                 self.value_dim, self.chunk, self.scale)
+                                 self.value_dim, self.chunk, self.scale, tiles=tiles.view(-1, 4) if tiles is not None else None)
         out = ctx.buffer("tattn.out", (t, self.width), self.dtype)
         return self.k.linear(attn, self.o, out, defer=True)

@@ -112,6 +112,38 @@ def test_talking_attention(K, dtype, heads, kv_heads, dim, vdim, page, chunk):
     close(out, want, dtype)
 
 
+def tiles_of(seqs, tile=16):
+    out, row = [], 0
+    for b, (n, rows) in enumerate(seqs):
+        for s in range(0, rows, tile):
+            out.append([row + s, min(tile, rows - s), n - rows + s, b])
+        row += rows
+    return i32(out)
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page,chunk", [(4, 2, 16, 24, 16, 16), (6, 6, 32, 32, 8, 32), (1, 1, 16, 8, 4, 128),
+                                                                (20, 5, 48, 16, 4, 8), (8, 4, 96, 80, 16, 48), (32, 8, 128, 128, 16, 64),
+                                                                (3, 3, 64, 8, 32, 100), (32, 4, 64, 64, 32, 64)])
+def test_talking_attention_tiles_on_the_tensor_core(K, heads, kv_heads, dim, vdim, page, chunk):
+    """The form that takes a tile of queries at a time (bfloat16): portions that start and end inside chunks, tiles that
+    cross a chunk's edge, tiles of one row, beside single decoded tokens; against the restatement and the one-token kernel."""
+    c = chunk
+    seqs = [(3 * c + 5, 2 * c + 3), (c, 1), (c + 1, 1), (1, 1), (2 * c + c // 2 + 40, 37), (5 * c, 1), (17, 17), (c + 9, 16)]
+    cache, meta, q = paged_case(torch.bfloat16, heads, kv_heads, dim, vdim, page, seqs, seed=heads + chunk)
+    talk = (torch.eye(heads) + 0.3 * torch.randn(heads, heads)).to(DEV)
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], device=DEV)
+    scale = dim ** -0.5
+    assert K.lib.llm_talking_attention_mma_supported(heads, kv_heads, dim, vdim, chunk, cache.shape[1])
+    want = R.ref_talking_attention(q, cache, meta.block_table, meta.token_request, meta.positions, talk, slopes, heads, kv_heads,
+                                   dim, vdim, page, chunk, scale)
+    out = torch.full((q.shape[0], heads * vdim), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K.talking_attention(q, cache, meta, talk, slopes, out, heads, kv_heads, dim, vdim, chunk, scale, tiles=tiles_of(seqs))
+    close(out, want, torch.bfloat16)
+    one = torch.empty_like(out)
+    K.talking_attention(q, cache, meta, talk, slopes, one, heads, kv_heads, dim, vdim, chunk, scale)
+    close(out, one, torch.bfloat16, "against the one-token kernel")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_talking_attention_edges_of_a_chunk(K, dtype):
     """The key just before a chunk's first position lines up with every query and would take all the weight if it were
@@ -135,7 +167,8 @@ def test_talking_attention_edges_of_a_chunk(K, dtype):
     want = R.ref_talking_attention(q, cache, meta.block_table, meta.token_request, meta.positions, talk, slopes, heads, kv_heads,
                                    dim, vdim, page, chunk, 0.25)
     out = torch.empty(n, heads * vdim, device=DEV, dtype=dtype)
-    K.talking_attention(q, cache, meta, talk, slopes, out, heads, kv_heads, dim, vdim, chunk, 0.25)
+    K.talking_attention(q, cache, meta, talk, slopes, out, heads, kv_heads, dim, vdim, chunk, 0.25,
+                        tiles=tiles_of([(n, n)]) if dtype == torch.bfloat16 else None)      # bfloat16: the tensor-core form
     others = torch.ones(n, dtype=torch.bool, device=DEV)
     others[[chunk - 1, 2 * chunk - 1]] = False           # (the planted key's own position sees it: the last key of its own chunk)
     assert out[others].float().abs().max() < 100         # no query of the next chunk saw the key just outside

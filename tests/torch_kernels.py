@@ -278,7 +278,7 @@ class TorchKernels:
             state[slot] = rows
         return q_out
 
-    def talking_attention(self, q, cache, meta, talk, slopes, out, heads, kv_heads, head_dim, value_dim, chunk, scale):
+    def talking_attention(self, q, cache, meta, talk, slopes, out, heads, kv_heads, head_dim, value_dim, chunk, scale, tiles=None):
         ps = cache.shape[1] // (kv_heads * (head_dim + value_dim))
         out.copy_(ref_talking_attention(q, cache, meta.block_table, meta.token_request, meta.positions, talk, slopes,
                                         heads, kv_heads, head_dim, value_dim, ps, chunk, scale))
