@@ -35,7 +35,7 @@ def i32(x):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,own", [(3, 1, 12, 20, 4, True), (4, 2, 16, 8, 2, True), (2, 2, 24, 24, 6, False),
-                                                              (8, 8, 96, 64, 1, True), (5, 5, 8, 8, 0, True)])
+                                                              (8, 8, 96, 64, 1, True), (5, 5, 8, 8, 0, True), (3, 1, 5, 7, 3, True)])
 def test_conv_norm_store(K, dtype, heads, kv_heads, dim, vdim, taps, own):
     torch.manual_seed(heads * 100 + taps)
     lens = [5, 1, 2, 9]                       # requests that bring fewer tokens than taps - 1 keep part of their old state
@@ -177,7 +177,7 @@ def test_talking_attention_edges_of_a_chunk(K, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim,vdim,rot", [(2, 32, 48, 32), (1, 20, 12, 10), (3, 24, 40, 24), (4, 8, 16, 0), (2, 64, 128, 32), (2, 160, 40, 64), (40, 32, 128, 32), (80, 32, 128, 0)])
+@pytest.mark.parametrize("heads,dim,vdim,rot", [(2, 32, 48, 32), (1, 20, 12, 10), (3, 24, 40, 24), (4, 8, 16, 0), (2, 64, 128, 32), (2, 160, 40, 64), (40, 32, 128, 32), (80, 32, 128, 0), (2, 18, 10, 6), (3, 7, 5, 0)])
 def test_retention_scan(K, dtype, heads, dim, vdim, rot):
     torch.manual_seed(dim)
     lens = [37, 1, 2, 18]
@@ -234,6 +234,17 @@ def test_retention_long_portions_in_segments(K, dtype, heads, dim, vdim, rot, le
     for slot, S in new.items():
         close(st[slot], S, torch.float32, "state")
     assert torch.equal(st[0], state[0]) and torch.equal(st[B + 1], state[B + 1])
+
+
+def test_retention_plain_form_in_segments(K):
+    """Sizes that are no multiples of 4 take the form without a register tile; long portions of it are walked in segments too."""
+    test_retention_long_portions_in_segments(K, torch.float32, 3, 18, 10, 6, [700, 300, 5, 129])
+    before = K.retention_segments
+    K.retention_segments = 4          # the measurement switch: the plain form for sizes the register tile would take
+    try:
+        test_retention_long_portions_in_segments(K, torch.bfloat16, 3, 32, 16, 16, [700, 300, 5, 129])
+    finally:
+        K.retention_segments = before
 
 
 def test_retention_keeps_a_far_key(K):
