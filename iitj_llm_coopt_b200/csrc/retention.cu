@@ -346,6 +346,19 @@ retention_tile_kernel(const T* __restrict__ proj, int proj_stride, const float* 
                 vs[idx] = (idx % cpb) < vcols ? to_f32(rawv[idx]) : 0.f;
             __syncthreads();
         }
+        // second pass: what these tokens hold so far is asked for now and added to after the walk (four 16-byte pieces a thread
+        // this way; a block wider than that takes the rest the slow way)
+        float4 held[4];
+        const int pieces = nb * (cpb >> 2);
+        if (MODE == 1) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = threadIdx.x + u * kThreads;
+                const int tt = idx / (cpb >> 2), x = (idx % (cpb >> 2)) << 2;
+                if (idx < pieces && x < vcols)
+                    held[u] = *reinterpret_cast<const float4*>(out + (size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c0 + x);
+            }
+        }
         for (int tt = 0; tt < nb; ++tt) {
             float part[4] = {0.f, 0.f, 0.f, 0.f};
             float v4[4];
@@ -405,9 +418,23 @@ retention_tile_kernel(const T* __restrict__ proj, int proj_stride, const float* 
         if (MODE == 1) {
             // what this block of tokens is to be given, added with all loads in flight at once
             __syncthreads();
-            for (int idx = threadIdx.x; idx < nb * cpb; idx += blockDim.x) {
-                const int tt = idx / cpb, x = idx % cpb;
-                if (x < vcols) out[(size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c0 + x] += vs[idx];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = threadIdx.x + u * kThreads;
+                const int tt = idx / (cpb >> 2), x = (idx % (cpb >> 2)) << 2;
+                if (idx < pieces && x < vcols) {
+                    const float4 add = *reinterpret_cast<const float4*>(vs + tt * cpb + x);
+                    held[u].x += add.x; held[u].y += add.y; held[u].z += add.z; held[u].w += add.w;
+                    *reinterpret_cast<float4*>(out + (size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c0 + x) = held[u];
+                }
+            }
+            for (int idx = threadIdx.x + 4 * kThreads; idx < pieces; idx += kThreads) {
+                const int tt = idx / (cpb >> 2), x = (idx % (cpb >> 2)) << 2;
+                if (x < vcols) {
+                    float* o4 = out + (size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + c0 + x;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o4[e] += vs[tt * cpb + x + e];
+                }
             }
         }
     }
