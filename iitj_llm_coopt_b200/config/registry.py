@@ -42,11 +42,16 @@ def load_config(model_dir: str):
     with open(path, encoding="utf-8") as f:
         raw = json.load(f)
     arch = architecture_for(raw)
-    return arch, arch.config_class.from_dict(raw)
+    cfg = arch.config_class.from_dict(raw)
+    if hasattr(cfg, "with_checkpoint_shapes"):
+        # a family may leave a size to a tensor's shape: the checkpoint's names and shapes (no data is read)
+        from ..weights.loader import checkpoint_index
+        cfg = cfg.with_checkpoint_shapes({name: rec[1] for name, rec in checkpoint_index(model_dir).items()})
+    return arch, cfg
 
 
 def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import lifusun, llama  # noqa: F401  (they register themselves)
+        from ..models import lifusun, llama, rodapel  # noqa: F401  (they register themselves)

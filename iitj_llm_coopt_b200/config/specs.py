@@ -30,6 +30,7 @@ class PositionSpec:
     theta: float = 10000.0
     scaling: tuple = ()          # sorted (name, value) pairs of the scaling law, () if none
     max_position: int = 0
+    pairing: str = "half"        # which numbers rotate together: "half" (i with i + rotary_dim/2) or "interleaved" (2i with 2i + 1)
 
     def scaling_dict(self) -> dict:
         return dict(self.scaling)
@@ -44,6 +45,8 @@ class CacheNeed:
         value_dim == 0: values are as wide as keys and a page is [2, kv_heads, page, head_dim];
         value_dim > 0: a value head has `value_dim` numbers and a page is one flat row, the
         key plane [kv_heads, page, head_dim] followed by the value plane [kv_heads, page, value_dim].
+        shared_value: the values are the leading `value_dim` numbers of the key rows themselves (one latent row per
+        token that serves as key and as value); a page is then the key plane alone.
     kind "state":    a fixed-size record per request (`state_shape`, `state_dtype`).
     kind "none":     nothing.
     Layers whose needs compare equal share one group of the cache manager.
@@ -55,9 +58,12 @@ class CacheNeed:
     state_shape: tuple = ()
     state_dtype: str = "float32"
     value_dim: int = 0
+    shared_value: bool = False
 
     def page_elements(self, page_size: int) -> int:
         """Numbers one page of one cache entry holds."""
+        if self.shared_value:
+            return self.kv_heads * page_size * self.head_dim
         return self.kv_heads * page_size * (self.head_dim + (self.value_dim or self.head_dim))
 
 

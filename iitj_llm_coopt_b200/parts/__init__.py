@@ -8,21 +8,26 @@ family an arrangement declares for each of its part names and by the `kind` of t
 from __future__ import annotations
 
 from .base import ParamSpec, Part, StepPlan, StepShape
-from .block import Arrangement, PreNormBlock, PreNormMixerBlock
-from .embedding import Embedding, OutputHead
-from .feed_forward import SwiGLU
+from .block import Arrangement, BranchNormBlock, BranchNormMixerBlock, PreNormBlock, PreNormMixerBlock
+from .embedding import Embedding, NormedEmbedding, OutputHead
+from .feed_forward import ClampedGLU, RoutedGLU, SwiGLU
+from .gated_attention import GatedAttention
+from .latent_attention import LatentAttention
 from .mixer import PagedAttention
 from .retention import Retention
 from .talking_attention import TalkingAttention
+from .wkv import WKV
 from .norm import RMSNorm, ScalarGainRMSNorm
 from .position import NoPosition, RotaryEmbedding, rope_inverse_frequencies
 
 NORMS = {"rmsnorm": RMSNorm, "rmsnorm_scalar": ScalarGainRMSNorm}
 POSITION_ENCODINGS = {"rope": RotaryEmbedding, "none": NoPosition}
-MIXERS = {"attention": PagedAttention, "talking_attention": TalkingAttention, "retention": Retention}
-FEED_FORWARDS = {"swiglu": SwiGLU}
-ARRANGEMENTS = {"prenorm": PreNormBlock, "prenorm_mixer": PreNormMixerBlock}
-EMBEDDINGS = {"table": Embedding}
+MIXERS = {"attention": PagedAttention, "talking_attention": TalkingAttention, "retention": Retention,
+          "latent_attention": LatentAttention, "gated_attention": GatedAttention, "wkv": WKV}
+FEED_FORWARDS = {"swiglu": SwiGLU, "clamped_glu": ClampedGLU, "routed_glu": RoutedGLU}
+ARRANGEMENTS = {"prenorm": PreNormBlock, "prenorm_mixer": PreNormMixerBlock, "branchnorm": BranchNormBlock,
+                "branchnorm_mixer": BranchNormMixerBlock}
+EMBEDDINGS = {"table": Embedding, "table_norm": NormedEmbedding}
 HEADS = {"linear": OutputHead}
 
 # family name (what an arrangement's PARTS declares for a part name) -> registry

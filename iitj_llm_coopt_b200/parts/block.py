@@ -6,6 +6,10 @@ hands them over as keywords.  At most one part of an arrangement is of family "m
 entry.  `forward(ctx, residual, delta, call)` returns the new (residual, delta): the residual stream stays apart in
 float32, and a sub-layer's output travels as a `delta` that the next norm adds into the residual before it normalises.
 
+`BranchNormBlock` puts the norms on the sub-layers' outputs: the sub-layers read the residual stream itself (as the
+engine's type), and  residual += mixer_norm(mixer(residual));  residual += feed_forward_norm(feed_forward(residual)).
+Nothing is left over for the next layer, so its delta is None.
+
 `PreNormBlock` (the reference's decoder layer, engine/model.py:192-211 and its fused form 230-253):
 
     x = mixer_norm(residual += delta_in);        a = mixer(x)
@@ -13,6 +17,7 @@ float32, and a sub-layer's output travels as a `delta` that the next norm adds i
 """
 from __future__ import annotations
 
+from ..kernels import materialize
 from .base import delta_for
 
 
@@ -64,3 +69,50 @@ class PreNormMixerBlock(Arrangement):
     def forward(self, ctx, residual, delta, call):
         x = self.mixer_norm.forward(ctx, residual, delta_for(self.mixer_norm, delta))
         return residual, self.mixer.forward(ctx, x, call)
+
+
+class BranchNormBlock(Arrangement):
+    """Norms on the branches:  residual += mixer_norm(mixer(residual));  residual += feed_forward_norm(feed_forward(residual)).
+    The sub-layers read the stream as the engine's type: in float32 that is the stream itself, in bfloat16 a rounded copy
+    that the kernel which adds a normed branch writes on the way (`Kernels.norm_add`)."""
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
+    CAST = "residual.cast"          # name of the rounded copy in the step's workspace and in `ctx.shared`
+
+    def _stream(self, ctx, residual, delta):
+        """(the stream with a pending delta of an earlier layer added, its copy of the engine's type)"""
+        dtype = self.mixer.dtype
+        if delta is not None:
+            residual.add_(delta_for(None, delta))
+            ctx.shared.pop(self.CAST, None)
+        if dtype == residual.dtype:
+            return residual
+        x = ctx.shared.get(self.CAST)
+        if x is None:
+            x = ctx.buffer(self.CAST, tuple(residual.shape), dtype)
+            x.copy_(residual)
+            ctx.shared[self.CAST] = x
+        return x
+
+    def _add_branch(self, ctx, residual, branch, norm):
+        dtype = self.mixer.dtype
+        cast = None if dtype == residual.dtype else ctx.buffer(self.CAST, tuple(residual.shape), dtype)
+        norm.k.norm_add(residual, materialize(branch), norm.weight, norm.eps, cast_out=cast)
+        if cast is not None:
+            ctx.shared[self.CAST] = cast
+        return residual if cast is None else cast
+
+    def forward(self, ctx, residual, delta, call):
+        x = self._stream(ctx, residual, delta)
+        x = self._add_branch(ctx, residual, self.mixer.forward(ctx, x, call), self.mixer_norm)
+        self._add_branch(ctx, residual, self.feed_forward.forward(ctx, x), self.feed_forward_norm)
+        return residual, None
+
+
+class BranchNormMixerBlock(BranchNormBlock):
+    """The same without a feed-forward."""
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    def forward(self, ctx, residual, delta, call):
+        x = self._stream(ctx, residual, delta)
+        self._add_branch(ctx, residual, self.mixer.forward(ctx, x, call), self.mixer_norm)
+        return residual, None

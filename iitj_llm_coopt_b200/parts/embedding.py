@@ -27,6 +27,33 @@ class Embedding(Part):
         return self.k.embed(ctx.token_ids, self.weight, out, self.scale)
 
 
+class NormedEmbedding(Embedding):
+    """x = rmsnorm(table[token_ids]) * norm: a norm with a gain per channel on the looked-up rows, statistics in
+    float32 (`eps` among the spec's options).  In a bfloat16 engine the rounded copy of the stream that the first layer
+    reads is written on the way (shared as BranchNormBlock.CAST)."""
+
+    def __init__(self, spec, kernels, dtype=None):
+        super().__init__(spec, kernels, dtype)
+        self.eps = float(dict(spec.options).get("eps", 1e-6))
+        self.dtype = dtype
+        self.norm = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        return {"weight": ParamSpec((spec.vocab, spec.width), kind="table"), "norm": ParamSpec((spec.width,), kind="vector")}
+
+    def forward(self, ctx):
+        raw = ctx.buffer("embedding.raw", (ctx.num_tokens, self.width), torch.float32)
+        self.k.embed(ctx.token_ids, self.weight, raw, self.scale)
+        out = ctx.buffer("residual", (ctx.num_tokens, self.width), torch.float32)
+        cast = None
+        if self.dtype is not None and self.dtype != torch.float32:
+            cast = ctx.buffer("residual.cast", (ctx.num_tokens, self.width), self.dtype)
+            ctx.shared["residual.cast"] = cast
+        self.k.norm_add(out, raw, self.norm, self.eps, cast_out=cast, accumulate=False)
+        return out
+
+
 class OutputHead(Part):
     graph_safe = True
 

@@ -5,6 +5,8 @@ gate and up stored as one [2*inner, width] matrix, gate rows first (engine/model
 """
 from __future__ import annotations
 
+import torch
+
 from .base import ParamSpec, Part
 
 
@@ -31,3 +33,91 @@ class SwiGLU(Part):
         self.k.linear(x, self.gate_up, act, swiglu=True)
         out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
         return self.k.linear(act, self.down, out, defer=True)
+
+
+class ClampedGLU(Part):
+    """A gated feed-forward with clamped branches and a sigmoid gate of a given slope:
+
+        g = min(x Wgate^T, limit),  u = clamp(x Wup^T, -limit, limit),  y = g * sigmoid(slope * g) * (u + 1),  out = y Wdown^T
+
+    `limit` and `slope` are options of the spec; gate and up are stored as one [2*inner, width] matrix, gate rows first."""
+    graph_safe = True
+
+    def __init__(self, spec, kernels, dtype):
+        self.spec, self.k, self.dtype = spec, kernels, dtype
+        self.width, self.inner = spec.width, spec.inner
+        self.limit, self.slope = float(spec.option("limit", 0.0)), float(spec.option("slope", 1.0))
+        self.gate_up = self.down = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        return {
+            "gate_up": ParamSpec((2 * spec.inner, spec.width), pieces=(("gate", spec.inner), ("up", spec.inner))),
+            "down": ParamSpec((spec.width, spec.inner)),
+        }
+
+    def forward(self, ctx, x):
+        t = x.shape[0]
+        gu = ctx.buffer("ffn.gate_up", (t, 2 * self.inner), self.dtype)
+        self.k.linear(x, self.gate_up, gu)
+        act = ctx.buffer("ffn.act", (t, self.inner), self.dtype)
+        self.k.glu_clamped(gu, act, self.limit, self.slope)
+        out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
+        return self.k.linear(act, self.down, out)
+
+
+class RoutedGLU(Part):
+    """A mixture of `experts` small ClampedGLU feed-forwards of which each token uses `experts_per_token`.
+
+        z = x Wrouter^T  (float32),  s = softmax(z) over all router outputs,  chosen = the top entries of s + correction,
+        out = sum over the chosen e of s[e] * expert_e(x)            (the weights are not renormalised)
+
+    The last `identity` router outputs stand for experts without tensors that hand their input back (s[e] * x).
+    Rows are sorted by expert on the device (`Kernels.moe_plan`), the experts' products run as one grouped product each
+    (the first reads its rows through the sorted index, applies the gate in its epilogue), and the chosen experts'
+    outputs of a token are added in the order of its choices, so a token's result does not depend on the batch."""
+    graph_safe = True
+
+    def __init__(self, spec, kernels, dtype):
+        self.spec, self.k, self.dtype = spec, kernels, dtype
+        self.width, self.inner = spec.width, spec.inner
+        self.experts, self.top = int(spec.experts), int(spec.experts_per_token)
+        self.identity = int(spec.option("identity", 0))
+        self.limit, self.slope = float(spec.option("limit", 0.0)), float(spec.option("slope", 1.0))
+        self.router = self.correction = self.expert_gate_up = self.expert_down = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        e, ff, w = int(spec.experts), spec.inner, spec.width
+        outputs = e + int(spec.option("identity", 0))
+        out = {"router": ParamSpec((outputs, w)), "correction": ParamSpec((outputs,), kind="vector")}
+        if e:
+            out["expert_gate_up"] = ParamSpec((e * 2 * ff, w), pieces=tuple(
+                (f"e{j}.{name}", ff) for j in range(e) for name in ("gate", "up")))
+            out["expert_down"] = ParamSpec((e * w, ff), pieces=tuple((f"e{j}.down", w) for j in range(e)))
+        return out
+
+    def load(self, tensors: dict) -> None:
+        super().load(tensors)
+        self.correction = self.correction.float().contiguous()
+
+    def forward(self, ctx, x):
+        t = x.shape[0]
+        scores = ctx.buffer("moe.scores", (t, self.experts + self.identity), torch.float32)
+        self.k.linear(x, self.router, scores)
+        chosen = ctx.buffer("moe.chosen", (t, self.top), torch.int32)
+        weights = ctx.buffer("moe.weights", (t, self.top), torch.float32)
+        self.k.route_topk(scores, self.correction, chosen, weights)
+        out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
+        plan = y = None
+        if self.experts:
+            rows = t * self.top
+            plan = self.k.moe_plan(chosen, self.experts, ctx.buffer("moe.source", (rows,), torch.int32),
+                                   ctx.buffer("moe.place", (rows,), torch.int32),
+                                   ctx.buffer("moe.tiles", (self.k.moe_tile_bound(rows, self.experts) + 1, 4), torch.int32))
+            act = ctx.buffer("moe.act", (t * self.top, self.inner), self.dtype)
+            self.k.moe_linear(x, self.expert_gate_up.view(self.experts, 2 * self.inner, self.width), act, plan, gather=True,
+                              glu=True, limit=self.limit, slope=self.slope)
+            y = ctx.buffer("moe.y", (t * self.top, self.width), self.dtype)
+            self.k.moe_linear(act, self.expert_down.view(self.experts, self.width, self.inner), y, plan)
+        return self.k.moe_combine(y, plan, chosen, weights, x, self.experts, out)

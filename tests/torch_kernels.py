@@ -185,6 +185,148 @@ def ref_headnorm_gate(o, gate, heads, value_dim, eps):
     return x.reshape(T, heads * value_dim) * torch.nn.functional.silu(gate.float())
 
 
+
+# ---- the Rodapel family's kernels ------------------------------------------------------------------------------
+
+def ref_norm_add(residual, branch, weight, eps, accumulate=True):
+    """residual (+)= rmsnorm(branch) * weight, float32."""
+    b = branch.float()
+    y = b * torch.rsqrt(b.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    return residual.float() + y if accumulate else y
+
+
+def ref_glu_clamped(gu, limit, slope):
+    n = gu.shape[1] // 2
+    g = torch.clamp(gu[:, :n].float(), max=limit)
+    u = torch.clamp(gu[:, n:].float(), -limit, limit)
+    return g * torch.sigmoid(slope * g) * (u + 1.0)
+
+
+def ref_rotate(v, cos, sin, dims, interleaved):
+    """v [T, n, D] float32: the leading `dims` numbers of each row rotated; cos / sin [T, dims / 2]."""
+    out = v.clone()
+    if not dims:
+        return out
+    c, s = cos.float().unsqueeze(1), sin.float().unsqueeze(1)
+    half = dims // 2
+    if interleaved:
+        a, b = v[..., 0:dims:2], v[..., 1:dims:2]
+        out[..., 0:dims:2] = a * c - b * s
+        out[..., 1:dims:2] = b * c + a * s
+    else:
+        a, b = v[..., :half], v[..., half:dims]
+        out[..., :half] = a * c - b * s
+        out[..., half:dims] = b * c + a * s
+    return out
+
+
+def ref_latent_prepare(qd, cos, sin, rotary_dim, interleaved, gain, eps, heads, dim, rot_dim, rank):
+    """Returns (rotated query parts [T, H, rot_dim], cache rows [T, rank + rot_dim]) in float32."""
+    T = qd.shape[0]
+    x = qd.float()
+    q = x[:, :heads * (dim + rot_dim)].view(T, heads, dim + rot_dim)
+    d = x[:, heads * (dim + rot_dim):]
+    lat = d[:, :rank]
+    lat = lat * torch.rsqrt(lat.pow(2).mean(-1, keepdim=True) + eps) * gain.float()
+    kr = ref_rotate(d[:, rank:].reshape(T, 1, rot_dim), cos, sin, rotary_dim, interleaved)[:, 0]
+    qr = ref_rotate(q[..., dim:].contiguous(), cos, sin, rotary_dim, interleaved)
+    return qr, torch.cat([lat, kr], dim=1)
+
+
+def ref_headnorm(qkv, q_gain, k_gain, eps, heads, kv_heads, dim, vdim):
+    """(q [T, H, D] normed, k [T, G, D] normed, v [T, G, V]) float32; gains None: no norm."""
+    T = qkv.shape[0]
+    x = qkv.float()
+    q = x[:, :heads * dim].view(T, heads, dim)
+    k = x[:, heads * dim:(heads + kv_heads) * dim].view(T, kv_heads, dim)
+    v = x[:, (heads + kv_heads) * dim:].view(T, kv_heads, vdim)
+    if q_gain is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_gain.float()
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_gain.float()
+    return q, k, v
+
+
+def flat_planes(cache, kv_heads, key_dim, value_dim, shared_value):
+    """(key plane [pages, G, page, Dk], value plane [pages, G, page, Dv]) of a flat-page cache entry."""
+    per = kv_heads * (key_dim if shared_value else key_dim + value_dim)
+    ps = cache.shape[1] // per
+    kplane = cache[:, :kv_heads * ps * key_dim].view(-1, kv_heads, ps, key_dim)
+    vplane = kplane[..., :value_dim] if shared_value else cache[:, kv_heads * ps * key_dim:].view(-1, kv_heads, ps, value_dim)
+    return kplane, vplane, ps
+
+
+def ref_attention_flat(q, q_stride_heads, cache, block_table, token_request, positions, heads, kv_heads, key_dim, value_dim,
+                       shared_value, window, scale, gate=None):
+    """q [T, >= heads * key_dim] (query heads first); returns [T, heads * value_dim] float32."""
+    T = q.shape[0]
+    kplane, vplane, ps = flat_planes(cache, kv_heads, key_dim, value_dim, shared_value)
+    group = heads // kv_heads
+    out = torch.zeros(T, heads, value_dim, dtype=torch.float32, device=q.device)
+    for t in range(T):
+        pos = int(positions[t])
+        lo = max(0, pos - window + 1) if window > 0 else 0
+        idx = torch.arange(lo, pos + 1, device=q.device)
+        table = block_table[int(token_request[t])]
+        pages, offs = table[(idx // ps).long()].long(), (idx % ps).long()
+        k = kplane[pages, :, offs, :].float().repeat_interleave(group, dim=1)
+        v = vplane[pages, :, offs, :].float().repeat_interleave(group, dim=1)
+        qt = q[t, :heads * key_dim].float().view(heads, key_dim)
+        p = torch.softmax(torch.einsum("hd,nhd->hn", qt, k) * scale, dim=-1)
+        o = torch.einsum("hn,nhv->hv", p, v)
+        if gate is not None:
+            o = o * torch.sigmoid(gate[t].float()).view(heads, 1)
+        out[t] = o
+    return out.view(T, heads * value_dim)
+
+
+def ref_route_topk(scores, correction, top):
+    s = torch.softmax(scores.float(), dim=-1)
+    chosen = torch.topk(s + correction.float(), top, dim=-1).indices
+    return chosen.to(torch.int32), torch.gather(s, 1, chosen)
+
+
+def ref_token_shift(x, mu, before, state_slots, cu_seqlens):
+    """[streams * T, w] float32: m_s = x + (x' - x) * mu_s, x' the row before (a request's first row of the step: its state)."""
+    T, w = x.shape
+    xf = x.float()
+    prev = torch.zeros_like(xf)
+    cu = [int(c) for c in cu_seqlens]
+    for b in range(len(cu) - 1):
+        lo, hi = cu[b], cu[b + 1]
+        if hi > lo:
+            prev[lo] = before[int(state_slots[b])].float()
+            prev[lo + 1:hi] = xf[lo:hi - 1]
+    m = mu.float().view(-1, 1, w)
+    return (xf + (prev - xf) * m).reshape(-1, w)
+
+
+def ref_wkv_decay(low, w2, w0):
+    return torch.exp(-torch.exp(torch.tanh(low.float()) @ w2.float().t() + w0.float()))
+
+
+def ref_wkv_scan(rkvg, decay, u, gain, eps, state, state_slots, cu_seqlens, heads, dim):
+    """rkvg [T, 4 * H * D]; state [slots, H, D (key), D (value)] float32.  Returns (gated output [T, H * D], {slot: new state})."""
+    T = rkvg.shape[0]
+    n = heads * dim
+    x = rkvg.float()
+    r, k, v = (x[:, i * n:(i + 1) * n].view(T, heads, dim) for i in range(3))
+    g = torch.nn.functional.silu(x[:, 3 * n:])
+    w = decay.float().view(T, heads, dim)
+    o = torch.zeros(T, heads, dim, dtype=torch.float32, device=rkvg.device)
+    new = {}
+    cu = [int(c) for c in cu_seqlens]
+    for b in range(len(cu) - 1):
+        slot = int(state_slots[b])
+        S = state[slot].float().clone()
+        for t in range(cu[b], cu[b + 1]):
+            kv = k[t].unsqueeze(2) * v[t].unsqueeze(1)
+            o[t] = torch.einsum("hi,hij->hj", r[t], S + u.float().unsqueeze(2) * kv)
+            S = w[t].unsqueeze(2) * S + kv
+        new[slot] = S
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+    return o.reshape(T, n) * gain.float() * g, new
+
+
 _M64 = np.uint64(0xFFFFFFFFFFFFFFFF)
 
 
@@ -297,6 +439,128 @@ class TorchKernels:
 
     def headnorm_gate(self, o, proj, gate_col, out, heads, value_dim, eps):
         out.copy_(ref_headnorm_gate(o, proj[:, gate_col:gate_col + heads * value_dim], heads, value_dim, eps))
+        return out
+
+    # ---- the Rodapel family ---------------------------------------------------------------------------------
+    MOE_TILE_ROWS = 64
+
+    def norm_add(self, residual, branch, weight, eps, cast_out=None, accumulate=True):
+        residual.copy_(ref_norm_add(residual, branch, weight, eps, accumulate))
+        if cast_out is not None:
+            cast_out.copy_(residual)
+        return residual
+
+    def glu_clamped(self, gu, act, limit, slope):
+        act.copy_(ref_glu_clamped(gu, limit, slope))
+        return act
+
+    def linear_by_group(self, a, w, out, a_stride, out_stride, a_offset=0, out_offset=0):
+        groups, n, k = w.shape
+        rows, lda = out.shape[0], a.shape[1]
+        flat = a.reshape(-1)
+        for g in range(groups):
+            ag = torch.as_strided(flat, (rows, k), (lda, 1), a_offset + g * a_stride)
+            out[:, out_offset + g * out_stride:out_offset + g * out_stride + n] = ag.float() @ w[g].float().t()
+        return out
+
+    def latent_prepare(self, qd, tables, rotary_dim, interleaved, gain, eps, q_out, cache, slots, heads, dim, rot_dim, rank):
+        cos, sin = tables if tables is not None else (None, None)
+        qr, rows = ref_latent_prepare(qd, cos, sin, rotary_dim, interleaved, gain, eps, heads, dim, rot_dim, rank)
+        T = qd.shape[0]
+        q_out.view(T, heads, rank + rot_dim)[..., rank:] = qr.to(q_out.dtype)
+        if slots is not None:
+            kplane, _, ps = flat_planes(cache, 1, rank + rot_dim, rank, True)
+            for t in range(T):
+                p, o = divmod(int(slots[t]), ps)
+                kplane[p, 0, o, :] = rows[t].to(cache.dtype)
+
+    def headnorm_store(self, qkv, q_gain, k_gain, eps, cache, slots, heads, kv_heads, dim, vdim):
+        q, k, v = ref_headnorm(qkv, q_gain, k_gain, eps, heads, kv_heads, dim, vdim)
+        T = qkv.shape[0]
+        qkv[:, :heads * dim] = q.reshape(T, -1).to(qkv.dtype)
+        if slots is not None:
+            kplane, vplane, ps = flat_planes(cache, kv_heads, dim, vdim, False)
+            for t in range(T):
+                p, o = divmod(int(slots[t]), ps)
+                kplane[p, :, o, :] = k[t].to(cache.dtype)
+                vplane[p, :, o, :] = v[t].to(cache.dtype)
+
+    def attention_flat(self, q, cache, meta, out, heads, kv_heads, key_dim, value_dim, shared_value=False, window=0, scale=1.0,
+                       gate=None):
+        out.copy_(ref_attention_flat(q, None, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
+                                     key_dim, value_dim, shared_value, window, scale, gate))
+        return out
+
+    def route_topk(self, scores, correction, chosen, weights):
+        c, w = ref_route_topk(scores, correction, chosen.shape[1])
+        chosen.copy_(c)
+        weights.copy_(w)
+
+    def moe_tile_bound(self, rows, experts):
+        return -(-rows // self.MOE_TILE_ROWS) + experts
+
+    def moe_plan(self, chosen, experts, source, place, tiles):
+        """Rows (token, choice) sorted by expert: source[r] = token of sorted row r, place[token * top + j] = its sorted row
+        (-1 for an expert without tensors), tiles[0, 0] = count, tiles[1 + i] = (expert, first row, rows, 0)."""
+        top = chosen.shape[1]
+        flat = chosen.reshape(-1).tolist()
+        order = sorted((e, i) for i, e in enumerate(flat) if e < experts)
+        place.fill_(-1)
+        recs, start = [], 0
+        for r, (e, i) in enumerate(order):
+            source[r] = i // top
+            place[i] = r
+        for e in range(experts):
+            n = sum(1 for x, _ in order if x == e)
+            for s in range(0, n, self.MOE_TILE_ROWS):
+                recs.append((e, start + s, min(self.MOE_TILE_ROWS, n - s), 0))
+            start += n
+        tiles.zero_()
+        tiles[0, 0] = len(recs)
+        for i, rec in enumerate(recs):
+            tiles[1 + i] = torch.tensor(rec, dtype=torch.int32)
+        return {"source": source, "place": place, "tiles": tiles, "rows": len(order)}
+
+    def moe_linear(self, a, w, out, plan, gather=False, glu=False, limit=0.0, slope=1.0):
+        tiles = plan["tiles"]
+        for i in range(int(tiles[0, 0])):
+            e, r0, n, _ = (int(v) for v in tiles[1 + i])
+            rows = plan["source"][r0:r0 + n].long() if gather else torch.arange(r0, r0 + n)
+            y = a[rows].float() @ w[e].float().t()
+            out[r0:r0 + n] = ref_glu_clamped(y, limit, slope) if glu else y
+        return out
+
+    def moe_combine(self, y, plan, chosen, weights, x, experts, out):
+        T, top = chosen.shape
+        acc = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
+        for t in range(T):
+            for j in range(top):
+                e = int(chosen[t, j])
+                row = x[t].float() if e >= experts else y[int(plan["place"][t * top + j])].float()
+                acc[t] += float(weights[t, j]) * row
+        out.copy_(acc)
+        return out
+
+    def token_shift(self, x, mu, before, state_slots, token_request, cu_seqlens, out):
+        out.copy_(ref_token_shift(x, mu, before, state_slots, cu_seqlens))
+        return out
+
+    def wkv_decay(self, low, w2, w0, out):
+        out.copy_(ref_wkv_decay(low, w2, w0))
+        return out
+
+    def wkv_scan(self, rkvg, decay, u, gain, eps, state, state_slots, cu_seqlens, out, heads, dim, write=True, last_rows=None):
+        got, new = ref_wkv_scan(rkvg, decay, u, gain, eps, state, state_slots, cu_seqlens, heads, dim)
+        out.copy_(got)
+        if write:
+            for slot, S in new.items():
+                state[slot] = S
+        if last_rows is not None:
+            x, before = last_rows
+            cu = [int(c) for c in cu_seqlens]
+            for b in range(len(cu) - 1):
+                if cu[b + 1] > cu[b]:
+                    before[int(state_slots[b])] = x[cu[b + 1] - 1].float()
         return out
 
     health_codes = (0, 0, 0, 0)     # what `sample` reports as the library's health words (tests set a failure here)
