@@ -1,0 +1,168 @@
+// The wkv mixer: a matrix state per head with a decay per key channel that each token chooses.
+//
+// llm_token_shift:  m_s[t] = x[t] + (x'[t] - x[t]) * mu_s for every stream s, x' the row before (for a request's first row of
+//                   the step: the row its state slot holds; zero for a new request).  out [streams * T, width].
+// llm_wkv_decay:    w[t, c] = exp(-exp(W2[c, :] . tanh(low[t, :]) + w0[c])), all float32.
+// llm_wkv_scan:     per (request, head), token by token in order:
+//                       o_t[j] = sum_i r_t[i] * (S[i][j] + u[i] * k_t[i] * v_t[j]);   S[i][j] = w_t[i] * S[i][j] + k_t[i] * v_t[j]
+//                   then each head's o divided by its root mean square, times gain, times silu(g).  S [head_dim (key i),
+//                   head_dim (value j)] float32 is read from and left in the request's state slot; thread j keeps column j in
+//                   registers.  Sixteen tokens' r, k, w, v rows are staged in shared memory at a time; the head norm of those
+//                   sixteen tokens runs after their walk, a warp per token.  The walk is strictly sequential in one order, so
+//                   how a prompt was cut into steps does not change a single bit.  With `x` and `before` the request's last row
+//                   of the step becomes the row its next step shifts in.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kChunk = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mu, const float* __restrict__ before,
+                   const int* __restrict__ state_slots, const int* __restrict__ token_request, const int* __restrict__ cu_seqlens,
+                   T* __restrict__ out, int tokens, int width, int streams) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = token_request[t];
+    const bool first = t == cu_seqlens[b];
+    const float* prev_state = before + (size_t)state_slots[b] * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = to_f32(x[(size_t)t * width + c]);
+        const float p = first ? prev_state[c] : to_f32(x[(size_t)(t - 1) * width + c]);
+        for (int s = 0; s < streams; ++s)
+            out[((size_t)s * tokens + t) * width + c] = from_f32<T>(v + (p - v) * mu[(size_t)s * width + c]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+wkv_decay_kernel(const float* __restrict__ low, const float* __restrict__ w2, const float* __restrict__ w0, float* __restrict__ out,
+                 int channels, int rank) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float th[];
+    const size_t t = blockIdx.x;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(low[t * rank + j]);
+    __syncthreads();
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const float* row = w2 + (size_t)c * rank;
+        float acc = 0.f;
+        for (int j = 0; j < rank; ++j) acc = fmaf(row[j], th[j], acc);
+        out[t * channels + c] = expf(-expf(acc + w0[c]));
+    }
+}
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(DMAX)
+wkv_scan_kernel(const T* __restrict__ rkvg, const float* __restrict__ decay, const float* __restrict__ u, const float* __restrict__ gain,
+                float eps, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
+                T* __restrict__ out, int heads, int dim, int write, const T* __restrict__ x, float* __restrict__ before, int width) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) float sr[kChunk][DMAX], sk[kChunk][DMAX], sw[kChunk][DMAX], sv[kChunk][DMAX], so[kChunk][DMAX];
+    __shared__ __align__(16) float su[DMAX];
+    const int b = blockIdx.x / heads, h = blockIdx.x % heads;
+    const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
+    if (hi <= lo) return;
+    const int j = threadIdx.x;
+    const bool own = j < dim;
+    const int n = heads * dim;
+    float* S = state + ((size_t)state_slots[b] * heads + h) * dim * dim;
+    float col[DMAX];
+#pragma unroll
+    for (int i = 0; i < DMAX; ++i) col[i] = own && i < dim ? S[(size_t)i * dim + j] : 0.f;
+    if (own) su[j] = u[(size_t)h * dim + j];
+    const int warp = j >> 5, lane = j & 31, nwarp = DMAX >> 5;
+    for (int t0 = lo; t0 < hi; t0 += kChunk) {
+        const int cnt = min(kChunk, hi - t0);
+        __syncthreads();                                  // the norm phase of the chunk before is done with so
+        if (own)
+            for (int c = 0; c < cnt; ++c) {
+                const size_t row = (size_t)(t0 + c) * 4 * n + (size_t)h * dim + j;
+                sr[c][j] = to_f32(rkvg[row]);
+                sk[c][j] = to_f32(rkvg[row + n]);
+                sv[c][j] = to_f32(rkvg[row + 2 * n]);
+                sw[c][j] = decay[(size_t)(t0 + c) * n + (size_t)h * dim + j];
+            }
+        __syncthreads();
+        if (own)
+            for (int c = 0; c < cnt; ++c) {
+                const float vj = sv[c][j];
+                float o = 0.f;
+#pragma unroll
+                for (int i = 0; i < DMAX; ++i) {
+                    if (i < dim) {
+                        const float kv = sk[c][i] * vj;
+                        o = fmaf(sr[c][i], fmaf(su[i], kv, col[i]), o);
+                        col[i] = fmaf(sw[c][i], col[i], kv);
+                    }
+                }
+                so[c][j] = o;
+            }
+        __syncthreads();
+        for (int c = warp; c < cnt; c += nwarp) {         // head norm, gain and gate: a warp per token
+            float ss = 0.f;
+            for (int i = lane; i < dim; i += 32) ss += so[c][i] * so[c][i];
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+            for (int i = lane; i < dim; i += 32) {
+                const size_t ch = (size_t)h * dim + i;
+                const float g = to_f32(rkvg[(size_t)(t0 + c) * 4 * n + 3 * n + ch]);
+                out[(size_t)(t0 + c) * n + ch] = from_f32<T>(so[c][i] * inv * gain[ch] * (g / (1.0f + expf(-g))));
+            }
+        }
+    }
+    if (write && own)
+#pragma unroll
+        for (int i = 0; i < DMAX; ++i)
+            if (i < dim) S[(size_t)i * dim + j] = col[i];
+    if (before && h == 0)
+        for (int c = j; c < width; c += DMAX) before[(size_t)state_slots[b] * width + c] = to_f32(x[(size_t)(hi - 1) * width + c]);
+}
+
+}  // namespace
+
+LLM_API int llm_token_shift(const void* x, const float* mu, const float* before, const int* state_slots, const int* token_request,
+                            const int* cu_seqlens, void* out, int dtype, int tokens, int width, int streams, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        llm_launch(token_shift_kernel<T>, (unsigned)tokens, 256, 0, stream, (const T*)x, mu, before, state_slots, token_request,
+                   cu_seqlens, (T*)out, tokens, width, streams);
+        LLM_CHECK_LAUNCH("token_shift");
+        return 0;
+    });
+}
+
+LLM_API int llm_wkv_decay(const float* low, const float* w2, const float* w0, float* out, int tokens, int channels, int rank,
+                          cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if ((size_t)rank * sizeof(float) > 48 * 1024) LLM_FAIL(-1, "wkv_decay: rank %d is too large", rank);
+    llm_launch(wkv_decay_kernel, (unsigned)tokens, 256, (size_t)rank * sizeof(float), stream, low, w2, w0, out, channels, rank);
+    LLM_CHECK_LAUNCH("wkv_decay");
+    return 0;
+}
+
+// rkvg [tokens, 4 * heads * dim] of `dtype` (r, k, v, g column blocks); decay [tokens, heads * dim] float32; state
+// [slots, heads, dim, dim] float32.  x [tokens, width] and before [slots, width] (or null): the shifted-in row to leave behind.
+LLM_API int llm_wkv_scan(const void* rkvg, const float* decay, const float* u, const float* gain, float eps, float* state,
+                         const int* state_slots, const int* cu_seqlens, void* out, int dtype, int requests, int heads, int dim,
+                         int write, const void* x, float* before, int width, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    if (dim <= 0 || dim > 128) LLM_FAIL(-1, "wkv_scan: head size %d must be in [1, 128]", dim);
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        const unsigned blocks = (unsigned)requests * heads;
+#define LLM_WKV_CASE(DMAX)                                                                                                   \
+        llm_launch(wkv_scan_kernel<T, DMAX>, blocks, DMAX, 0, stream, (const T*)rkvg, decay, u, gain, eps, state, state_slots,   \
+                   cu_seqlens, (T*)out, heads, dim, write, (const T*)x, before, width)
+        if (dim <= 32) LLM_WKV_CASE(32);
+        else if (dim <= 64) LLM_WKV_CASE(64);
+        else LLM_WKV_CASE(128);
+#undef LLM_WKV_CASE
+        LLM_CHECK_LAUNCH("wkv_scan");
+        return 0;
+    });
+}
+
+LLM_TRACE_EXPORT(wkv)

@@ -101,6 +101,28 @@ _SIGNATURES = {
                            ctypes.c_longlong, _c_void_p, _c_int, _c_int, _c_void_p],
     "llm_retention_headnorm_gate": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                     _c_void_p],
+    "llm_norm_add": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+    "llm_glu_clamped": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
+    "llm_latent_prepare": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p,
+                           _c_void_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_headnorm_store": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, ctypes.c_longlong, _c_int,
+                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_attention_flat": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                           _c_void_p],
+    "llm_gemm_grouped_tile_rows": [],
+    "llm_gemm_grouped": [_c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p,
+                         ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int,
+                         _c_void_p, _c_int, _c_int, _c_float, _c_float, _c_void_p],
+    "llm_route_topk": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
+    "llm_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                        _c_void_p],
+    "llm_token_shift": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                        _c_void_p],
+    "llm_wkv_decay": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_wkv_scan": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                     _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p],
 }
 
 # The library's health words in the order llm_sample copies them out (csrc/common.cuh): which kernel, and what its codes mean.
@@ -762,6 +784,251 @@ class Kernels:
               gate_col + heads * value_dim <= proj.shape[1], "headnorm_gate: shapes do not fit")
         self._call("llm_retention_headnorm_gate", _ptr(o), proj.data_ptr() + gate_col * proj.element_size(), proj.shape[1],
                    _ptr(out), DTYPE_CODE[proj.dtype], tokens, heads, value_dim, float(eps), self._stream())
+        return out
+
+    # ---- branch norms, gated feed-forwards with clamps, routed experts ------------------------------------------
+    def norm_add(self, residual, branch, weight, eps, cast_out=None, accumulate: bool = True):
+        """residual (+)= rmsnorm(branch) * weight with float32 statistics (csrc/branch_norm.cu); `cast_out`: a copy of the new
+        residual in another type (what the next sub-layer reads).  `accumulate` False writes the normed rows instead."""
+        _check(residual, "norm_add.residual", torch.float32, 2)
+        _check(branch, "norm_add.branch", tuple(DTYPE_CODE), 2)
+        _check(weight, "norm_add.weight", tuple(DTYPE_CODE), 1)
+        tokens, width = residual.shape
+        _need(tuple(branch.shape) == (tokens, width) and weight.shape[0] == width, "norm_add: shapes differ")
+        if cast_out is not None:
+            _check(cast_out, "norm_add.cast_out", tuple(DTYPE_CODE), 2)
+            _need(cast_out.shape == residual.shape, "norm_add.cast_out: shape differs from residual")
+        self._call("llm_norm_add", _ptr(residual), _ptr(branch), DTYPE_CODE[branch.dtype], _ptr(weight), DTYPE_CODE[weight.dtype],
+                   _ptr(cast_out), DTYPE_CODE[cast_out.dtype] if cast_out is not None else 0, tokens, width, float(eps),
+                   1 if accumulate else 0, self._stream())
+        return residual
+
+    def glu_clamped(self, gu, act, limit: float, slope: float):
+        """act = g * sigmoid(slope * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gu [T, 2 * inner]
+        holds the gate columns, then the up columns."""
+        _check(gu, "glu_clamped.gu", tuple(DTYPE_CODE), 2)
+        _check(act, "glu_clamped.act", gu.dtype, 2)
+        _need(gu.shape[1] == 2 * act.shape[1] and gu.shape[0] == act.shape[0], "glu_clamped: shapes do not fit")
+        self._call("llm_glu_clamped", _ptr(gu), _ptr(act), DTYPE_CODE[gu.dtype], act.shape[0], act.shape[1], float(limit),
+                   float(slope), self._stream())
+        return act
+
+    def linear_by_group(self, a, w, out, a_stride: int, out_stride: int, a_offset: int = 0, out_offset: int = 0):
+        """One product per group in one launch (csrc/gemm_grouped.cu): with w [groups, n, k] and rows = out.shape[0],
+        out[:, out_offset + g * out_stride : ... + n] = A_g . w[g]^T, where row r of A_g starts at element
+        a_offset + g * a_stride + r * a.shape[1] of `a` (a head's slice of a wider row, or a block of rows of its own)."""
+        _check(a, "linear_by_group.a", tuple(DTYPE_CODE), 2)
+        _check(w, "linear_by_group.w", a.dtype, 3)
+        _check(out, "linear_by_group.out", a.dtype, 2)
+        groups, n, k = w.shape
+        rows, lda = out.shape[0], a.shape[1]
+        _need(a_offset + (groups - 1) * a_stride + (rows - 1) * lda + k <= a.numel(), "linear_by_group: a is too small")
+        _need(out_offset + (groups - 1) * out_stride + n <= out.shape[1], "linear_by_group: out is too narrow")
+        self._call("llm_gemm_grouped", _ptr(a), lda, int(a_stride), int(a_offset), None, _ptr(w), _ptr(out), out.shape[1],
+                   int(out_stride), int(out_offset), DTYPE_CODE[a.dtype], rows, n, k, groups, None, 0, 0, 0.0, 0.0, self._stream())
+        return out
+
+    def route_topk(self, scores, correction, chosen, weights):
+        """Router outputs [T, R] float32 -> chosen [T, top] int32 (the largest softmax(scores) + correction, descending)
+        and weights [T, top] float32 (their softmax values); csrc/moe_route.cu."""
+        _check(scores, "route_topk.scores", torch.float32, 2)
+        _check(correction, "route_topk.correction", torch.float32, 1)
+        _check(chosen, "route_topk.chosen", torch.int32, 2)
+        _check(weights, "route_topk.weights", torch.float32, 2)
+        tokens, outputs = scores.shape
+        _need(correction.shape[0] == outputs and chosen.shape[0] == tokens and tuple(weights.shape) == tuple(chosen.shape),
+              "route_topk: shapes do not fit")
+        self._call("llm_route_topk", _ptr(scores), _ptr(correction), _ptr(chosen), _ptr(weights), tokens, outputs, chosen.shape[1],
+                   self._stream())
+
+    def moe_tile_bound(self, rows: int, experts: int) -> int:
+        """The most row tiles `moe_plan` can make of `rows` (token, choice) pairs over `experts` experts."""
+        return -(-rows // self.lib.llm_gemm_grouped_tile_rows()) + experts
+
+    def moe_plan(self, chosen, experts: int, source, place, tiles):
+        """Sorts the (token, choice) pairs of `chosen` [T, top] by expert on the device: source [T * top] (token of each
+        sorted row), place [T * top] (sorted row of each pair, -1 for a choice >= experts), tiles [bound + 1, 4] (count in
+        front, then (expert, first row, rows) records).  Returns what `moe_linear` and `moe_combine` take as `plan`."""
+        _check(chosen, "moe_plan.chosen", torch.int32, 2)
+        for name, t in (("source", source), ("place", place)):
+            _check(t, "moe_plan." + name, torch.int32, 1)
+            _need(t.shape[0] == chosen.numel(), f"moe_plan.{name}: one entry per (token, choice)")
+        _check(tiles, "moe_plan.tiles", torch.int32, 2)
+        bound = self.moe_tile_bound(chosen.numel(), experts)
+        _need(tiles.shape[1] == 4 and tiles.shape[0] >= bound + 1, "moe_plan.tiles: [tile bound + 1, 4]")
+        self._call("llm_moe_plan", _ptr(chosen), chosen.numel(), chosen.shape[1], int(experts),
+                   self.lib.llm_gemm_grouped_tile_rows(), _ptr(source), _ptr(place), _ptr(tiles), bound, self._stream())
+        return {"source": source, "place": place, "tiles": tiles, "bound": bound}
+
+    def moe_linear(self, a, w, out, plan, gather: bool = False, glu: bool = False, limit: float = 0.0, slope: float = 1.0):
+        """out[r] = a[row of r] . w[expert of r]^T for every sorted row r of `plan`; with `gather` a's rows are tokens
+        (read through plan["source"]), else sorted rows.  `glu`: w [E, 2n, k] holds gate rows then up rows and the clamped
+        gate is applied in the epilogue."""
+        _check(a, "moe_linear.a", tuple(DTYPE_CODE), 2)
+        _check(w, "moe_linear.w", a.dtype, 3)
+        _check(out, "moe_linear.out", a.dtype, 2)
+        experts, wn, k = w.shape
+        n = wn // 2 if glu else wn
+        _need(a.shape[1] == k and out.shape[1] == n and out.shape[0] == plan["source"].shape[0], "moe_linear: shapes do not fit")
+        self._call("llm_gemm_grouped", _ptr(a), a.shape[1], 0, 0, _ptr(plan["source"]) if gather else None, _ptr(w), _ptr(out),
+                   out.shape[1], 0, 0, DTYPE_CODE[a.dtype], 0, n, k, experts, _ptr(plan["tiles"]), plan["bound"],
+                   1 if glu else 0, float(limit), float(slope), self._stream())
+        return out
+
+    def moe_combine(self, y, plan, chosen, weights, x, experts: int, out):
+        """out[t] = sum_j weights[t, j] * (y[sorted row of (t, j)], or x[t] where chosen[t, j] >= experts), j in order."""
+        _check(x, "moe_combine.x", tuple(DTYPE_CODE), 2)
+        _check(out, "moe_combine.out", x.dtype, 2)
+        _check(chosen, "moe_combine.chosen", torch.int32, 2)
+        _check(weights, "moe_combine.weights", torch.float32, 2)
+        _need(out.shape == x.shape and chosen.shape[0] == x.shape[0] and tuple(weights.shape) == tuple(chosen.shape),
+              "moe_combine: shapes do not fit")
+        if y is not None:
+            _check(y, "moe_combine.y", x.dtype, 2)
+            _need(y.shape[1] == x.shape[1], "moe_combine.y: width differs")
+        else:
+            _need(experts == 0, "moe_combine: experts without outputs")
+        self._call("llm_moe_combine", _ptr(y), _ptr(plan["place"]) if plan is not None else None, _ptr(chosen), _ptr(weights),
+                   _ptr(x), _ptr(out), DTYPE_CODE[x.dtype], x.shape[0], x.shape[1], chosen.shape[1], int(experts), self._stream())
+        return out
+
+    # ---- attention over flat pages (independent key and value sizes, latent rows), wkv ---------------------------
+    @staticmethod
+    def _flat_page_size(cache_layer, kv_heads, key_dim, value_dim, shared_value) -> int:
+        per_token = kv_heads * (key_dim if shared_value else key_dim + value_dim)
+        _need(cache_layer.dim() == 2 and cache_layer.shape[1] % per_token == 0,
+              f"cache: a page of {tuple(cache_layer.shape)} does not hold rows of {kv_heads} heads of {key_dim} (+ {value_dim})")
+        return cache_layer.shape[1] // per_token
+
+    def latent_prepare(self, qd, tables, rotary_dim, interleaved, gain, eps, q_out, cache_layer, slots, heads, dim, rot_dim, rank):
+        """From the fused projection qd [T, heads * (dim + rot_dim) + rank + rot_dim]: the latent part normed (gain [rank]
+        float32) and the shared key part rotated, stored together as one cache row per token at `slots` (None: no store);
+        every head's rotated query part written to q_out [T, heads * (rank + rot_dim)] behind the place of its absorbed
+        part.  tables = (cos, sin) float32 [T, rotary_dim / 2]; csrc/attention_flat.cu."""
+        _check(qd, "latent_prepare.qd", tuple(DTYPE_CODE), 2)
+        _check(q_out, "latent_prepare.q_out", qd.dtype, 2)
+        _check(gain, "latent_prepare.gain", torch.float32, 1)
+        tokens = qd.shape[0]
+        _need(qd.shape[1] == heads * (dim + rot_dim) + rank + rot_dim and gain.shape[0] == rank and
+              tuple(q_out.shape) == (tokens, heads * (rank + rot_dim)), "latent_prepare: shapes do not fit")
+        cos = sin = None
+        if rotary_dim:
+            cos, sin = tables
+            _check(cos, "latent_prepare.cos", torch.float32, 2)
+            _check(sin, "latent_prepare.sin", torch.float32, 2)
+            _need(cos.shape == (tokens, rotary_dim // 2) and sin.shape == cos.shape, "latent_prepare: tables must be [tokens, rotary_dim / 2]")
+        page_size, stride = 1, 0
+        if slots is not None:
+            _check(slots, "latent_prepare.slots", torch.int32, 1)
+            _check(cache_layer, "latent_prepare.cache", qd.dtype, 2)
+            _need(slots.shape[0] == tokens, "latent_prepare.slots: one per token")
+            page_size, stride = self._flat_page_size(cache_layer, 1, rank + rot_dim, rank, True), cache_layer.shape[1]
+        self._call("llm_latent_prepare", _ptr(qd), qd.shape[1], _ptr(cos), _ptr(sin), int(rotary_dim), 1 if interleaved else 0,
+                   _ptr(gain), float(eps), _ptr(q_out), _ptr(cache_layer) if slots is not None else None, _ptr(slots), stride,
+                   page_size, DTYPE_CODE[qd.dtype], tokens, heads, dim, rot_dim, rank, self._stream())
+
+    def headnorm_store(self, qkv, q_gain, k_gain, eps, cache_layer, slots, heads, kv_heads, dim, vdim):
+        """qkv [T, heads * dim + kv_heads * (dim + vdim)]: every query head (in place) and key head divided by its root
+        mean square and multiplied by a gain [dim] shared by all heads (None: no norm); keys and values stored at `slots`
+        in a flat-page cache (None: no store)."""
+        _check(qkv, "headnorm_store.qkv", tuple(DTYPE_CODE), 2)
+        tokens = qkv.shape[0]
+        _need(qkv.shape[1] == heads * dim + kv_heads * (dim + vdim), "headnorm_store.qkv: wrong width")
+        for name, g in (("q_gain", q_gain), ("k_gain", k_gain)):
+            if g is not None:
+                _check(g, "headnorm_store." + name, torch.float32, 1)
+                _need(g.shape[0] == dim, f"headnorm_store.{name}: one per head dim")
+        _need((q_gain is None) == (k_gain is None), "headnorm_store: both gains or none")
+        page_size, stride = 1, 0
+        if slots is not None:
+            _check(slots, "headnorm_store.slots", torch.int32, 1)
+            _check(cache_layer, "headnorm_store.cache", qkv.dtype, 2)
+            _need(slots.shape[0] == tokens, "headnorm_store.slots: one per token")
+            page_size, stride = self._flat_page_size(cache_layer, kv_heads, dim, vdim, False), cache_layer.shape[1]
+        self._call("llm_headnorm_store", _ptr(qkv), qkv.shape[1], _ptr(q_gain), _ptr(k_gain), float(eps),
+                   _ptr(cache_layer) if slots is not None else None, _ptr(slots), stride, page_size, DTYPE_CODE[qkv.dtype], tokens,
+                   heads, kv_heads, dim, vdim, self._stream())
+
+    def attention_flat(self, q, cache_layer, meta, out, heads, kv_heads, key_dim, value_dim, shared_value: bool = False,
+                       window: int = 0, scale: float = 1.0, gate=None):
+        """Attention of every token's query heads (the leading heads * key_dim numbers of q's rows) over the flat-page
+        cache of its request: keys of key_dim, values of value_dim (`shared_value`: the leading value_dim numbers of the key
+        rows), a sliding window (0: all earlier keys), optionally each head's output times sigmoid(gate[t, head])."""
+        _check(q, "attention_flat.q", tuple(DTYPE_CODE), 2)
+        _check(cache_layer, "attention_flat.cache", q.dtype, 2)
+        _check(out, "attention_flat.out", q.dtype, 2)
+        tokens = q.shape[0]
+        _need(q.shape[1] >= heads * key_dim and tuple(out.shape) == (tokens, heads * value_dim), "attention_flat: q / out shapes do not fit")
+        _check(meta.block_table, "attention_flat.block_table", torch.int32, 2)
+        _check(meta.token_request, "attention_flat.token_request", torch.int32, 1)
+        _check(meta.positions, "attention_flat.positions", torch.int32, 1)
+        _need(meta.token_request.shape[0] == tokens and meta.positions.shape[0] == tokens,
+              "attention_flat: one token_request and one position per token")
+        if gate is not None:
+            _check(gate, "attention_flat.gate", torch.float32, 2)
+            _need(tuple(gate.shape) == (tokens, heads), "attention_flat.gate: [tokens, heads]")
+        page_size = self._flat_page_size(cache_layer, kv_heads, key_dim, value_dim, shared_value)
+        self._call("llm_attention_flat", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
+                   meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(gate), _ptr(out), out.shape[1],
+                   DTYPE_CODE[q.dtype], tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size,
+                   int(window), float(scale), self._stream())
+        return out
+
+    def token_shift(self, x, mu, before, state_slots, token_request, cu_seqlens, out):
+        """out [streams * T, width]: m_s = x + (x' - x) * mu_s, mu [streams * width] float32, x' the row before (a request's
+        first row of the step: before[its state slot], float32 [slots, width]); csrc/wkv.cu."""
+        _check(x, "token_shift.x", tuple(DTYPE_CODE), 2)
+        _check(mu, "token_shift.mu", torch.float32, 1)
+        _check(before, "token_shift.before", torch.float32, 2)
+        _check(out, "token_shift.out", x.dtype, 2)
+        tokens, width = x.shape
+        streams = mu.shape[0] // width
+        _need(mu.shape[0] == streams * width and tuple(out.shape) == (streams * tokens, width) and before.shape[1] == width,
+              "token_shift: shapes do not fit")
+        for name, t in (("state_slots", state_slots), ("token_request", token_request), ("cu_seqlens", cu_seqlens)):
+            _check(t, "token_shift." + name, torch.int32, 1)
+        _need(token_request.shape[0] == tokens and cu_seqlens.shape[0] == state_slots.shape[0] + 1, "token_shift: index arrays do not fit")
+        self._call("llm_token_shift", _ptr(x), _ptr(mu), _ptr(before), _ptr(state_slots), _ptr(token_request), _ptr(cu_seqlens),
+                   _ptr(out), DTYPE_CODE[x.dtype], tokens, width, streams, self._stream())
+        return out
+
+    def wkv_decay(self, low, w2, w0, out):
+        """out[t, c] = exp(-exp(w2[c] . tanh(low[t]) + w0[c])), all float32."""
+        for name, t, d in (("low", low, 2), ("w2", w2, 2), ("w0", w0, 1), ("out", out, 2)):
+            _check(t, "wkv_decay." + name, torch.float32, d)
+        tokens, rank = low.shape
+        _need(w2.shape[1] == rank and w0.shape[0] == w2.shape[0] and tuple(out.shape) == (tokens, w2.shape[0]), "wkv_decay: shapes do not fit")
+        self._call("llm_wkv_decay", _ptr(low), _ptr(w2), _ptr(w0), _ptr(out), tokens, w2.shape[0], rank, self._stream())
+        return out
+
+    def wkv_scan(self, rkvg, decay, u, gain, eps, state, state_slots, cu_seqlens, out, heads, dim, write: bool = True,
+                 last_rows=None):
+        """The wkv walk with head norm, gain and gate (csrc/wkv.cu): rkvg [T, 4 * heads * dim] (r, k, v, g blocks), decay
+        [T, heads * dim] float32, u [heads, dim], gain [heads * dim], state [slots, heads, dim, dim] float32 (read, and with
+        `write` left at the step's last token).  last_rows = (x [T, width], before [slots, width]): each request's last row of
+        x becomes its row in `before`."""
+        _check(rkvg, "wkv_scan.rkvg", tuple(DTYPE_CODE), 2)
+        _check(out, "wkv_scan.out", rkvg.dtype, 2)
+        for name, t, d in (("decay", decay, 2), ("u", u, 2), ("gain", gain, 1), ("state", state, 4)):
+            _check(t, "wkv_scan." + name, torch.float32, d)
+        tokens, n = rkvg.shape[0], heads * dim
+        _need(rkvg.shape[1] == 4 * n and tuple(decay.shape) == (tokens, n) and tuple(out.shape) == (tokens, n) and
+              tuple(u.shape) == (heads, dim) and gain.shape[0] == n and tuple(state.shape[1:]) == (heads, dim, dim),
+              "wkv_scan: shapes do not fit")
+        _check(state_slots, "wkv_scan.state_slots", torch.int32, 1)
+        _check(cu_seqlens, "wkv_scan.cu_seqlens", torch.int32, 1)
+        _need(cu_seqlens.shape[0] == state_slots.shape[0] + 1, "wkv_scan.cu_seqlens: requests + 1 entries")
+        x = before = None
+        width = 0
+        if last_rows is not None:
+            x, before = last_rows
+            _check(x, "wkv_scan.x", rkvg.dtype, 2)
+            _check(before, "wkv_scan.before", torch.float32, 2)
+            width = x.shape[1]
+            _need(x.shape[0] == tokens and before.shape[1] == width, "wkv_scan.last_rows: shapes do not fit")
+        self._call("llm_wkv_scan", _ptr(rkvg), _ptr(decay), _ptr(u), _ptr(gain), float(eps), _ptr(state), _ptr(state_slots),
+                   _ptr(cu_seqlens), _ptr(out), DTYPE_CODE[rkvg.dtype], state_slots.shape[0], heads, dim, 1 if write else 0,
+                   _ptr(x), _ptr(before), width, self._stream())
         return out
 
     # ---- matrix products -------------------------------------------------------------

@@ -27,7 +27,7 @@ def parse_args(argv=None):
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-requests", type=int, default=16, help="most requests live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: most requests live at a time")
     ap.add_argument("--device", default="cuda:0")
     return ap.parse_args(argv)
 
