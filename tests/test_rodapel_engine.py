@@ -1,0 +1,162 @@
+"""The Rodapel family through the engine's step function, cache manager and entry points, against the plain restatement
+of tests/plain_rodapel.py: every way of cutting the same requests into steps (whole, the last tokens one by one, portions
+down to two tokens, mixed batches over a pool so small that pages and state slots are used again), the first tokens,
+long decoding across many windows and pages, and greedy generation through `LLM.generate`.
+CPU cases run the host logic with the plain-torch kernel double; `-m gpu` cases run the CUDA kernels.
+
+bfloat16 and routed experts.  A token whose two best choice scores lie closer together than bfloat16 rounding moves them
+may pick another expert than the float64 restatement does, and everything after it in the request then differs by far more
+than rounding: no tolerance makes that comparison meaningful.  So in bfloat16 the configurations are compared strictly with
+their routed feed-forwards replaced by dense ones of the same sizes (`dense_variant`), and as they are with a bound on the
+median error and on the share of positions beyond the tolerance; float32 is compared strictly, as it is."""
+import copy
+
+import pytest
+import torch
+
+import plain_rodapel as plain
+import replay_cases as cases
+from helpers import make_engine, rel_err, run_steps
+from rodapel_models import CONFIGS, write_model
+
+# float32: the kernel double on a CPU stays at a median of 1e-6 of the largest logit, with single positions up to 1.5e-4
+# where a head's wkv output or a branch is small before its norm; the tolerances were fixed from that run
+FP32_TOL, BF16_TOL = 3e-4, 3e-2
+LENGTHS = {"A": [1, 9, 10, 11, 33, 70], "B": [2, 31, 32, 33, 34, 97, 130], "C": [3, 40, 75], "D": [7, 15, 16, 17, 69, 70, 71, 130]}
+
+GPU = pytest.mark.gpu
+CASES = [pytest.param("cpu", "float32", n, id=f"cpu-fp32-{n}") for n in "ABCD"] + \
+        [pytest.param("cuda:0", dt, n, marks=GPU, id=f"gpu-{dt}-{n}") for dt in ("float32", "bfloat16") for n in "ABCD"]
+
+
+def dense_variant(cfg_and_ranks):
+    cfg, ranks = copy.deepcopy(cfg_and_ranks)
+    for lay in cfg["layers"]:
+        if lay["mlp"] is not None and lay["mlp"]["kind"] == "moe":
+            lay["mlp"] = {"kind": "dense", "ff": lay["mlp"]["expert"]["ff"], "limit": lay["mlp"]["expert"]["limit"]}
+    return cfg, ranks
+
+
+def has_experts(name):
+    return any(l["mlp"] is not None and l["mlp"]["kind"] == "moe" for l in CONFIGS[name][0][0]["layers"])
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    out = {}
+    for name, (cfg, seed, _) in CONFIGS.items():
+        out[name] = write_model(cfg, str(tmp_path_factory.mktemp(f"rod_{name}")), seed)
+        out[name + "-dense"] = write_model(dense_variant(cfg), str(tmp_path_factory.mktemp(f"rod_{name}_dense")), seed)
+    return out
+
+
+@pytest.fixture(scope="module")
+def refs(dirs):
+    out = {}
+    for key, d in dirs.items():
+        cfg, seed, _ = CONFIGS[key[0]]
+        reqs = cases.requests_for(cfg[0]["vocab"], LENGTHS[key[0]], seed + 10)
+        c, w = plain.read_model_dir(d)
+        out[key] = (reqs, {rid: plain.forward(c, w, toks).float() for rid, toks in reqs.items()})
+    return out
+
+
+def errors(rows, ref, reqs):
+    """Per position: largest difference of the logits row over the largest logit of the request."""
+    out = []
+    for rid, toks in reqs.items():
+        got = torch.stack([rows[(rid, i)] for i in range(len(toks))])
+        top = max(ref[rid].abs().max().item(), 1e-30)
+        out += ((got.float().cpu() - ref[rid]).abs().amax(dim=1) / top).tolist()
+    return out
+
+
+def compare(rows, ref, reqs, tol, strict=True):
+    e = sorted(errors(rows, ref, reqs))
+    if strict:
+        assert e[-1] <= tol, e[-1]
+    else:
+        assert e[len(e) // 2] <= tol / 3 and sum(1 for x in e if x > tol) <= 0.25 * len(e), (e[len(e) // 2], e[-1])
+
+
+def variants(name, dtype):
+    """(model key, strict) pairs to run for a configuration in an engine type."""
+    if dtype == "float32" or not has_experts(name):
+        return [(name, True)]
+    return [(name + "-dense", True), (name, False)]
+
+
+@pytest.mark.parametrize("device,dtype,name", CASES)
+def test_every_way_of_cutting(dirs, refs, device, dtype, name):
+    page = CONFIGS[name][2]
+    tol = FP32_TOL if dtype == "float32" else BF16_TOL
+    for key, strict in variants(name, dtype):
+        reqs, ref = refs[key]
+        mixed_steps, peak = cases.mixed(reqs, live=3, seed=2)
+        pages = peak // page
+        eng = make_engine(dirs[key], dtype, page, pages, device=device, max_num_seqs=3, max_num_batched_tokens=peak)
+        for steps in (cases.whole(reqs), cases.last_one_by_one(reqs, tail=20), cases.portions(reqs), mixed_steps):
+            rows = run_steps(eng, steps)
+            eng.cache.check()
+            assert eng.cache.num_free == min(g.pool.num_pages for g in (eng.cache.groups[i] for i in eng.cache.paged)) \
+                if eng.cache.paged else True
+            assert len(eng.cache.free_slots) == 3
+            compare(rows, ref, reqs, tol, strict)
+
+
+@pytest.mark.parametrize("device,dtype,name", CASES)
+def test_first_tokens_and_token_by_token(dirs, refs, device, dtype, name):
+    """A whole request one token a step: nothing before position 0 (a zero row shifted in, an empty state, a window
+    that reaches before the start)."""
+    page = CONFIGS[name][2]
+    for key, strict in variants(name, dtype):
+        reqs, ref = refs[key]
+        rid, toks = max(reqs.items(), key=lambda kv: len(kv[1]) if len(kv[1]) <= 40 else 0)
+        eng = make_engine(dirs[key], dtype, page, 16, device=device, max_num_seqs=2)
+        rows = run_steps(eng, [([(rid, toks[i:i + 1], [0])], []) for i in range(len(toks))])
+        compare(rows, ref, {rid: toks}, FP32_TOL if dtype == "float32" else BF16_TOL, strict)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_long_decoding(dirs, dtype, name):
+    """A short prompt, then hundreds of tokens one by one through many windows and pages; every position compared."""
+    cfg, seed, page = CONFIGS[name]
+    total = 330
+    for key, strict in variants(name, dtype):
+        reqs = cases.requests_for(cfg[0]["vocab"], [total], seed + 20)
+        c, w = plain.read_model_dir(dirs[key])
+        ref = {rid: plain.forward(c, w, toks).float() for rid, toks in reqs.items()}
+        eng = make_engine(dirs[key], dtype, page, -(-total // page) + 1, max_num_seqs=2)
+        compare(run_steps(eng, cases.last_one_by_one(reqs, tail=total - 21)), ref, reqs, FP32_TOL if dtype == "float32" else BF16_TOL, strict)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_float32_cuts_agree_closely(dirs, refs, name):
+    reqs, _ = refs[name]
+    eng = make_engine(dirs[name], "float32", CONFIGS[name][2], 128, max_num_seqs=4)
+    a, b = run_steps(eng, cases.whole(reqs)), run_steps(eng, cases.portions(reqs))
+    assert max(rel_err(b[k], a[k]) for k in a) < 1e-5
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda:0", marks=GPU)])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_llm(dirs, device, name):
+    """Prompts of unequal length generate together through the scheduler (small token budget: prompts are cut into
+    portions, the pool is small enough that requests wait; on the GPU decode steps replay from CUDA graphs); float32 must
+    choose the plain implementation's tokens."""
+    from iitj_llm_coopt_b200 import LLM, SamplingParams
+    cfg, seed, page = CONFIGS[name]
+    c, w = plain.read_model_dir(dirs[name])
+    prompts = [[5, 17, 3, 120, 9], list(range(40, 77)), [129], list(range(20, 39))]
+    want = [plain.greedy_generate(c, w, p, 8) for p in prompts]
+    kernels = None
+    if device == "cpu":
+        from torch_kernels import TorchKernels
+        kernels = TorchKernels()
+    llm = LLM(dirs[name], dtype="float32", page_size=page, num_pages=128 // page, max_num_seqs=3, max_num_batched_tokens=24,
+              device=device, kernels=kernels)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    assert [o.token_ids for o in outs] == want

@@ -254,3 +254,43 @@ def test_wkv(K, dtype, heads, dim, width, rank):
         close(outs[0], outs[1], dtype)
         close(states[0], states[1], torch.float32)
         assert torch.equal(befores[0], befores[1])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window,page,total", [(16, 16, 70), (33, 8, 100), (1, 4, 9), (72, 16, 200), (0, 16, 700)])
+def test_planted_keys_at_the_window_s_edges(K, dtype, window, page, total):
+    """Random weights would hide a window that is one key off: here every query points along one axis, the key just outside a
+    query's window (with no window: key 3, hundreds of positions back) would take all the weight if it were seen (or, with no
+    window, must take it), and the first key inside carries a value of its own.  Queries are asked in a prompt portion and as
+    single decoded tokens, with windows that start on a page's first and last slot."""
+    heads, kv_heads, dim, vdim = 2, 1, 16, 8
+    per = kv_heads * (dim + vdim)
+    cache, table = paged(dtype, 1, [total], page, per, seed=window)
+    g = torch.Generator().manual_seed(5)
+    keys = torch.randn(total, dim, generator=g) * 0.1
+    vals = torch.randn(total, vdim, generator=g)
+    asked = sorted({total - 1, total - 2, min(total - 1, window + page - 1), min(total - 1, window + page), min(total - 1, 2 * page)})
+    for p in asked:
+        outside, first = (p - window, p - window + 1) if window else (None, 3)
+        if outside is not None and outside >= 0:
+            keys[outside, 0] = 40.0 + outside % 7
+        if first >= 0:
+            keys[first, 0] = max(keys[first, 0].item(), 8.0)
+            vals[first] = 5.0 + p % 3
+    kplane, vplane, ps = R.flat_planes(cache, kv_heads, dim, vdim, False)
+    for j in range(total):
+        pg, o = int(table[0, j // page]), j % page
+        kplane[pg, 0, o] = keys[j].to(dtype)
+        vplane[pg, 0, o] = vals[j].to(dtype)
+    RK = R.TorchKernels()
+    for rows in (asked, [asked[-1]]):                    # a portion of several queries, then one token alone
+        q = torch.zeros(len(rows), heads * dim, dtype=dtype, device="cuda")
+        q[:, 0], q[:, dim] = 1.0, 0.5
+        meta = meta_for(table, [0] * len(rows), rows)
+        out = torch.empty(len(rows), heads * vdim, dtype=dtype, device="cuda")
+        want = torch.empty(len(rows), heads * vdim, dtype=torch.float32, device="cuda")
+        K.attention_flat(q, cache, meta, out, heads, kv_heads, dim, vdim, window=window, scale=1.0)
+        RK.attention_flat(q, cache, meta, want, heads, kv_heads, dim, vdim, window=window, scale=1.0)
+        close(out, want, dtype)
+        if window:
+            assert (want[:, :vdim].amax(1) > 1.0).any()       # the planted value shows in the answer
