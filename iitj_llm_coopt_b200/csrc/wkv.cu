@@ -6,9 +6,10 @@
 // llm_wkv_scan:     per (request, head), token by token in order:
 //                       o_t[j] = sum_i r_t[i] * (S[i][j] + u[i] * k_t[i] * v_t[j]);   S[i][j] = w_t[i] * S[i][j] + k_t[i] * v_t[j]
 //                   then each head's o divided by its root mean square, times gain, times silu(g).  S [head_dim (key i),
-//                   head_dim (value j)] float32 is read from and left in the request's state slot; thread j keeps column j in
-//                   registers.  Sixteen tokens' r, k, w, v rows are staged in shared memory at a time; the head norm of those
-//                   sixteen tokens runs after their walk, a warp per token.  The walk is strictly sequential in one order, so
+//                   head_dim (value j)] float32 is read from and left in the request's state slot; four threads share column j
+//                   (a quarter of its rows each, in registers; their sums meet by two shuffles).  Sixteen tokens' r, k, v, g, w rows
+//                   (eight at head sizes above 64) are staged in shared memory at a time, asked for while the rows before them
+//                   are walked, and read as 16-byte pieces; the head norm of those tokens runs after their walk, a warp per token.  The walk is strictly sequential in one order, so
 //                   how a prompt was cut into steps does not change a single bit.  With `x` and `before` the request's last row
 //                   of the step becomes the row its next step shifts in.
 #include "common.cuh"
@@ -54,52 +55,82 @@ wkv_decay_kernel(const float* __restrict__ low, const float* __restrict__ w2, co
 }
 
 template <typename T, int DMAX>
-__global__ void __launch_bounds__(DMAX)
+__global__ void __launch_bounds__(DMAX * 4)
 wkv_scan_kernel(const T* __restrict__ rkvg, const float* __restrict__ decay, const float* __restrict__ u, const float* __restrict__ gain,
                 float eps, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
                 T* __restrict__ out, int heads, int dim, int write, const T* __restrict__ x, float* __restrict__ before, int width) {
     pdl_trigger();
     pdl_wait();
-    __shared__ __align__(16) float sr[kChunk][DMAX], sk[kChunk][DMAX], sw[kChunk][DMAX], sv[kChunk][DMAX], so[kChunk][DMAX];
+    // Four threads share a column j of S: thread (j, p) keeps the rows 16 q + 4 p + (0..3), q = 0 .. DMAX / 16 - 1, so the four
+    // read neighbouring 16-byte pieces of the staged rows (no bank conflict, and all columns read the same piece at once).
+    constexpr int R = DMAX / 4, THREADS = DMAX * 4;
+    constexpr int CH = DMAX > 64 ? kChunk / 2 : kChunk;          // tokens staged at a time
+    constexpr int PER = CH * DMAX / THREADS;                     // elements of each staged array a thread brings
+    __shared__ __align__(16) float sr[CH][DMAX], sk[CH][DMAX], sw[CH][DMAX], sv[CH][DMAX], sg[CH][DMAX], so[CH][DMAX];
     __shared__ __align__(16) float su[DMAX];
     const int b = blockIdx.x / heads, h = blockIdx.x % heads;
     const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
     if (hi <= lo) return;
-    const int j = threadIdx.x;
-    const bool own = j < dim;
+    const int tid = threadIdx.x, j = tid >> 2, p = tid & 3;
     const int n = heads * dim;
     float* S = state + ((size_t)state_slots[b] * heads + h) * dim * dim;
-    float col[DMAX];
+    float col[R];
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) col[i] = own && i < dim ? S[(size_t)i * dim + j] : 0.f;
-    if (own) su[j] = u[(size_t)h * dim + j];
-    const int warp = j >> 5, lane = j & 31, nwarp = DMAX >> 5;
-    for (int t0 = lo; t0 < hi; t0 += kChunk) {
-        const int cnt = min(kChunk, hi - t0);
-        __syncthreads();                                  // the norm phase of the chunk before is done with so
-        if (own)
-            for (int c = 0; c < cnt; ++c) {
-                const size_t row = (size_t)(t0 + c) * 4 * n + (size_t)h * dim + j;
-                sr[c][j] = to_f32(rkvg[row]);
-                sk[c][j] = to_f32(rkvg[row + n]);
-                sv[c][j] = to_f32(rkvg[row + 2 * n]);
-                sw[c][j] = decay[(size_t)(t0 + c) * n + (size_t)h * dim + j];
-            }
+    for (int q = 0; q < R / 4; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = 16 * q + 4 * p + e;
+            col[4 * q + e] = i < dim && j < dim ? S[(size_t)i * dim + j] : 0.f;
+        }
+    for (int i = tid; i < DMAX; i += THREADS) su[i] = i < dim ? u[(size_t)h * dim + i] : 0.f;
+    const int warp = tid >> 5, lane = tid & 31, nwarp = THREADS >> 5;
+    // A chunk's rows are asked for while the chunk before is walked (channels beyond dim are zero and stay out of every sum).
+    float lr[PER], lk[PER], lv[PER], lg[PER], lw[PER];
+    auto fetch = [&](int t0) {
+        const int cnt = min(CH, hi - t0);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int idx = tid + e * THREADS, c = idx / DMAX, i = idx % DMAX;
+            const bool live = c < cnt && i < dim;
+            const size_t row = (size_t)(t0 + c) * 4 * n + (size_t)h * dim + i;
+            lr[e] = live ? to_f32(rkvg[row]) : 0.f;
+            lk[e] = live ? to_f32(rkvg[row + n]) : 0.f;
+            lv[e] = live ? to_f32(rkvg[row + 2 * n]) : 0.f;
+            lg[e] = live ? to_f32(rkvg[row + 3 * n]) : 0.f;
+            lw[e] = live ? decay[(size_t)(t0 + c) * n + (size_t)h * dim + i] : 0.f;
+        }
+    };
+    fetch(lo);
+    for (int t0 = lo; t0 < hi; t0 += CH) {
+        const int cnt = min(CH, hi - t0);
+        __syncthreads();                                  // the norm phase of the chunk before is done with the staged rows
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int idx = tid + e * THREADS, c = idx / DMAX, i = idx % DMAX;
+            sr[c][i] = lr[e]; sk[c][i] = lk[e]; sv[c][i] = lv[e]; sg[c][i] = lg[e]; sw[c][i] = lw[e];
+        }
         __syncthreads();
-        if (own)
-            for (int c = 0; c < cnt; ++c) {
-                const float vj = sv[c][j];
-                float o = 0.f;
+        if (t0 + CH < hi) fetch(t0 + CH);
+        for (int c = 0; c < cnt; ++c) {
+            const float vj = sv[c][j];
+            float o = 0.f;
 #pragma unroll
-                for (int i = 0; i < DMAX; ++i) {
-                    if (i < dim) {
-                        const float kv = sk[c][i] * vj;
-                        o = fmaf(sr[c][i], fmaf(su[i], kv, col[i]), o);
-                        col[i] = fmaf(sw[c][i], col[i], kv);
-                    }
-                }
-                so[c][j] = o;
+            for (int q = 0; q < R / 4; ++q) {
+                const int base = 16 * q + 4 * p;
+                const float4 r4 = *reinterpret_cast<const float4*>(&sr[c][base]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&sk[c][base]);
+                const float4 w4 = *reinterpret_cast<const float4*>(&sw[c][base]);
+                const float4 u4 = *reinterpret_cast<const float4*>(&su[base]);
+                float kv;
+                kv = k4.x * vj; o = fmaf(r4.x, fmaf(u4.x, kv, col[4 * q]), o);     col[4 * q] = fmaf(w4.x, col[4 * q], kv);
+                kv = k4.y * vj; o = fmaf(r4.y, fmaf(u4.y, kv, col[4 * q + 1]), o); col[4 * q + 1] = fmaf(w4.y, col[4 * q + 1], kv);
+                kv = k4.z * vj; o = fmaf(r4.z, fmaf(u4.z, kv, col[4 * q + 2]), o); col[4 * q + 2] = fmaf(w4.z, col[4 * q + 2], kv);
+                kv = k4.w * vj; o = fmaf(r4.w, fmaf(u4.w, kv, col[4 * q + 3]), o); col[4 * q + 3] = fmaf(w4.w, col[4 * q + 3], kv);
             }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (p == 0) so[c][j] = o;
+        }
         __syncthreads();
         for (int c = warp; c < cnt; c += nwarp) {         // head norm, gain and gate: a warp per token
             float ss = 0.f;
@@ -107,17 +138,21 @@ wkv_scan_kernel(const T* __restrict__ rkvg, const float* __restrict__ decay, con
             const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
             for (int i = lane; i < dim; i += 32) {
                 const size_t ch = (size_t)h * dim + i;
-                const float g = to_f32(rkvg[(size_t)(t0 + c) * 4 * n + 3 * n + ch]);
+                const float g = sg[c][i];
                 out[(size_t)(t0 + c) * n + ch] = from_f32<T>(so[c][i] * inv * gain[ch] * (g / (1.0f + expf(-g))));
             }
         }
     }
-    if (write && own)
+    if (write && j < dim)
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i)
-            if (i < dim) S[(size_t)i * dim + j] = col[i];
+        for (int q = 0; q < R / 4; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 16 * q + 4 * p + e;
+                if (i < dim) S[(size_t)i * dim + j] = col[4 * q + e];
+            }
     if (before && h == 0)
-        for (int c = j; c < width; c += DMAX) before[(size_t)state_slots[b] * width + c] = to_f32(x[(size_t)(hi - 1) * width + c]);
+        for (int c = tid; c < width; c += THREADS) before[(size_t)state_slots[b] * width + c] = to_f32(x[(size_t)(hi - 1) * width + c]);
 }
 
 }  // namespace
@@ -154,7 +189,7 @@ LLM_API int llm_wkv_scan(const void* rkvg, const float* decay, const float* u, c
         using T = decltype(tag);
         const unsigned blocks = (unsigned)requests * heads;
 #define LLM_WKV_CASE(DMAX)                                                                                                   \
-        llm_launch(wkv_scan_kernel<T, DMAX>, blocks, DMAX, 0, stream, (const T*)rkvg, decay, u, gain, eps, state, state_slots,   \
+        llm_launch(wkv_scan_kernel<T, DMAX>, blocks, DMAX * 4, 0, stream, (const T*)rkvg, decay, u, gain, eps, state, state_slots,   \
                    cu_seqlens, (T*)out, heads, dim, write, (const T*)x, before, width)
         if (dim <= 32) LLM_WKV_CASE(32);
         else if (dim <= 64) LLM_WKV_CASE(64);

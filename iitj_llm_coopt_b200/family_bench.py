@@ -65,8 +65,9 @@ def _model_runs(name, config_dict, vocab, batch, context, steps, warmup, prefill
     ids = [f"d{i}" for i in range(batch)]
     for r in ids:
         cache.admit(r)
-        cache.ensure(r, context)
-        cache.advance(r, context)
+        for upto in list(range(prefill_tokens, context, prefill_tokens)) + [context]:     # as portions would fill it: a windowed
+            cache.ensure(r, upto)                                                        # group's pool holds windows, not contexts
+            cache.advance(r, upto)
     first = torch.randint(0, vocab, (batch,), generator=gen).tolist()
     prev, launches = None, 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -96,7 +97,7 @@ def _model_runs(name, config_dict, vocab, batch, context, steps, warmup, prefill
             "parameter_bytes": params}
 
 
-def _kernels_alone(lif, llama, tokens, batch, context, hbm_gbs, flush):
+def _kernels_alone_lifusun(lif, llama, tokens, batch, context, hbm_gbs, flush):
     """The family's kernels (and Llama's like ones) alone at the shapes of a `tokens`-token prompt and of a decode
     step of `batch` requests: microseconds, bytes that must move, fraction of the copy bandwidth."""
     import torch
@@ -189,6 +190,169 @@ def _kernels_alone(lif, llama, tokens, batch, context, hbm_gbs, flush):
         record(f"headnorm_gate ({label})", us, T * RH * RV * (4 + 2 + 2))
     return out
 
+def _kernels_alone_rodapel(cfg, llama, tokens, batch, context, hbm_gbs, flush):
+    """Rodapel's kernels (and Llama's like ones) alone at the shapes of a `tokens`-token prompt and of a decode step of
+    `batch` requests: microseconds, the bytes that must move and the fraction of the copy bandwidth that is, or for the
+    arithmetic-bound prompt attention the TFLOP/s of the causal scores and sums."""
+    import torch
+
+    from . import kernels as _k
+    K = _k.load()
+    dev, bf = "cuda", torch.bfloat16
+    att = next(l["mixer"] for l in cfg["layers"] if l["type"] == "attention")
+    lat = next(l["mixer"] for l in cfg["layers"] if l["type"] == "latent_attention")
+    rec = next(l["mixer"] for l in cfg["layers"] if l["type"] == "wkv")
+    moe = next(l["mlp"] for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
+    width = cfg["width"]
+    H, G, D, V, window = att["heads"], att["kv_heads"], att["dim"], att["vdim"], att["mask"]["size"]
+    LH, LD, LR, LC = lat["heads"], lat["dim"], lat["rot_dim"], lat["kv_rank"]
+    page = 16
+    out = []
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def record(name, us, nbytes=None, flops=None, like=None):
+        r = {"kernel": name, "us": round(us, 2)}
+        if nbytes is not None:
+            r.update(mbytes=round(nbytes / 1e6, 2), frac_of_copy_bandwidth=round(nbytes / (us * 1e-6) / (hbm_gbs * 1e9), 3))
+        if flops is not None:
+            r.update(tflops=round(flops / (us * 1e-6) / 1e12, 1))
+        if like:
+            r["like"] = like
+        out.append(r)
+
+    for label, T, B, per in (("prefill", tokens, 1, tokens), ("decode", batch, batch, 1)):
+        ctx_len = per if label == "prefill" else context
+        pages_per = -(-ctx_len // page)
+        cu, treq = [i * per for i in range(B + 1)], [b for b in range(B) for _ in range(per)]
+        pos = [ctx_len - per + i for _ in range(B) for i in range(per)]
+        table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+        slots = i32([int(table[b, p // page]) * page + p % page for b, p in zip(treq, pos)])
+        meta = SimpleNamespace(block_table=table, token_request=i32(treq), positions=i32(pos), query_lens=[per] * B,
+                               seq_lens_host=[ctx_len] * B, attention_plan=None)
+        from .parts.base import StepShape
+        from .parts.flat_tiles import plan_flat_tiles
+
+        def plan_for(heads, kv_heads, key_dim, value_dim, win):
+            plan = plan_flat_tiles(K, StepShape([per] * B, [ctx_len] * B, T, label == "decode", False, dev), heads, kv_heads,
+                                   key_dim, value_dim, win)
+            plan.bind({"tiles": i32(plan.arrays["tiles"])})
+            return plan
+        seen = sum(min(p + 1, window) for p in pos)                     # keys the windowed queries see, in all
+        causal = sum(p + 1 for p in pos)
+        # --- windowed attention: head norms + store, attention with the gate
+        qkv = torch.randn(T, H * D + G * (D + V), device=dev).to(bf)
+        cache = (torch.randn(B * pages_per + 1, G * page * (D + V), device=dev) * 0.5).to(bf)
+        gain = torch.ones(D, device=dev)
+        us = 1e3 * _timed(lambda: K.headnorm_store(qkv, gain, gain, 1e-6, cache, slots, H, G, D, V), 10, 3, flush)
+        record(f"headnorm_store ({label})", us, nbytes=T * (2 * H * D + 2 * G * (D + V)) * 2, like="llm_rope_store")
+        gate = torch.randn(T, H, device=dev)
+        ao = torch.empty(T, H * V, device=dev, dtype=bf)
+        wplan = plan_for(H, G, D, V, window)
+        us = 1e3 * _timed(lambda: K.attention_flat(qkv, cache, meta, ao, H, G, D, V, window=window, scale=D ** -0.5, gate=gate, plan=wplan), 5, 3, flush)
+        if label == "decode":
+            record(f"attention_flat, window {window} ({label})", us, nbytes=B * min(ctx_len, window) * G * (D + V) * 2, like="llama attention")
+        else:
+            record(f"attention_flat, window {window} ({label})", us, flops=2 * seen * H * (D + V), like="llama attention")
+        # --- Llama: rotation + store, attention over the whole context, the pre-norm
+        if D == V:
+            lqkv = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+            lcache = (torch.randn(B * pages_per + 1, 2, G, page, D, device=dev) * 0.5).to(bf)
+            inv = (1.0 / 500000.0 ** (torch.arange(0, D, 2, device=dev).float() / D)).contiguous()
+            posd = i32(pos)
+            us = 1e3 * _timed(lambda: K.rope_store(lqkv, posd, inv, slots, lcache, H, G, D, D), 10, 3, flush)
+            record(f"llm_rope_store ({label})", us, nbytes=T * (H + 2 * G) * D * 2 * 2)
+            lo = torch.empty(T, H * D, device=dev, dtype=bf)
+            meta.attention_plan = None
+            us = 1e3 * _timed(lambda: K.attention(lqkv, lcache, meta, lo, H, G, D), 10, 3, flush)
+            if label == "decode":
+                record(f"llama attention ({label})", us, nbytes=B * ctx_len * G * 2 * D * 2)
+            else:
+                record(f"llama attention ({label})", us, flops=4 * causal * H * D)
+        # --- latent attention: prepare + store, the absorbed queries, attention over the latent rows, the values' product
+        row = LC + LR
+        qd = torch.randn(T, LH * (LD + LR) + row, device=dev).to(bf)
+        lat_cache = (torch.randn(B * pages_per + 1, page * row, device=dev) * 0.5).to(bf)
+        ang = torch.tensor(pos, device=dev).float().unsqueeze(1) * (1.0 / 1e6 ** (torch.arange(LR // 2, device=dev).float() / (LR // 2)))
+        tabs = (ang.cos().contiguous(), ang.sin().contiguous())
+        lgain = torch.ones(LC, device=dev)
+        qa = torch.empty(T, LH * row, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.latent_prepare(qd, tabs, LR, True, lgain, 1e-6, qa, lat_cache, slots, LH, LD, LR, LC), 10, 3, flush)
+        record(f"latent_prepare ({label})", us, nbytes=T * (LH * (LD + 2 * LR) + 2 * row) * 2, like="llm_rope_store")
+        uk = (torch.randn(LH, LC, LD, device=dev) * LD ** -0.5).to(bf)
+        us = 1e3 * _timed(lambda: K.linear_by_group(qd, uk, qa, a_stride=LD + LR, out_stride=row), 10, 3, flush)
+        record(f"absorbed queries, a product per head ({label})", us, nbytes=(T * LH * (LD + LC) + LH * LC * LD) * 2,
+               flops=2 * T * LH * LD * LC)
+        lo2 = torch.empty(T, LH * LC, device=dev, dtype=bf)
+        lplan = plan_for(LH, 1, row, LC, 0)
+        us = 1e3 * _timed(lambda: K.attention_flat(qa, lat_cache, meta, lo2, LH, 1, row, LC, shared_value=True, scale=0.07, plan=lplan), 3, 3, flush)
+        if label == "decode":
+            record(f"attention_flat, latent rows ({label})", us, nbytes=B * ctx_len * row * 2, like="llama attention")
+        else:
+            record(f"attention_flat, latent rows ({label})", us, flops=2 * causal * LH * (row + LC), like="llama attention")
+        # --- wkv: shift, decay, walk
+        RH, RD = rec["heads"], rec["dim"]
+        n = RH * RD
+        x = torch.randn(T, width, device=dev).to(bf)
+        mu = torch.rand(5 * width, device=dev)
+        before = torch.zeros(B + 1, width, device=dev)
+        ss, cs, tr = i32(list(range(B))), i32(cu), i32(treq)
+        mixes = torch.empty(5 * T, width, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.token_shift(x, mu, before, ss, tr, cs, mixes), 10, 3, flush)
+        record(f"token_shift ({label})", us, nbytes=T * width * 2 * 6)
+        rkvg = torch.randn(T, 4 * n, device=dev).to(bf)
+        decay = torch.rand(T, n, device=dev) * 0.5 + 0.5
+        u, g1 = torch.randn(RH, RD, device=dev) * 0.3, torch.ones(n, device=dev)
+        state = torch.zeros(B + 1, RH, RD, RD, device=dev)
+        wo = torch.empty(T, n, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.wkv_scan(rkvg, decay, u, g1, 1e-6, state, ss, cs, wo, RH, RD), 5, 3, flush)
+        record(f"wkv_scan ({label})", us, nbytes=T * n * (4 * 2 + 4 + 2) + 2 * B * n * RD * 4, flops=4 * T * n * RD, like="retention_scan")
+        # --- routed experts: choice, sort, the two grouped products, the weighted sum
+        E, I, top, ff = moe["router"]["experts"], moe["router"]["identity"], moe["router"]["top"], moe["expert"]["ff"]
+        scores = torch.randn(T, E + I, device=dev)
+        corr = torch.zeros(E + I, device=dev)
+        chosen = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, top, device=dev)
+        us = 1e3 * _timed(lambda: K.route_topk(scores, corr, chosen, wts), 10, 3, flush)
+        record(f"route_topk ({label})", us)
+        rows = T * top
+        bufs = (torch.zeros(rows, dtype=torch.int32, device=dev), torch.zeros(rows, dtype=torch.int32, device=dev),
+                torch.zeros(K.moe_tile_bound(rows, E) + 1, 4, dtype=torch.int32, device=dev))
+        us = 1e3 * _timed(lambda: K.moe_plan(chosen, E, *bufs), 10, 3, flush)
+        record(f"moe_plan ({label})", us)
+        plan = K.moe_plan(chosen, E, *bufs)
+        w1 = (torch.randn(E, 2 * ff, width, device=dev) * width ** -0.5).to(bf)
+        w2 = (torch.randn(E, width, ff, device=dev) * ff ** -0.5).to(bf)
+        act = torch.empty(rows, ff, device=dev, dtype=bf)
+        y = torch.empty(rows, width, device=dev, dtype=bf)
+        live = int(plan["tiles"][0, 1])
+        us = 1e3 * _timed(lambda: K.moe_linear(x, w1, act, plan, gather=True, glu=True, limit=7.0, slope=1.702), 5, 3, flush)
+        record(f"experts' gate/up product with the gate ({label})", us, nbytes=w1.numel() * 2 + live * (width + ff) * 2,
+               flops=4 * live * ff * width, like="gate/up product (SwiGLU)")
+        us = 1e3 * _timed(lambda: K.moe_linear(act, w2, y, plan), 5, 3, flush)
+        record(f"experts' down product ({label})", us, nbytes=w2.numel() * 2 + live * (width + ff) * 2, flops=2 * live * ff * width,
+               like="down product")
+        mo = torch.empty(T, width, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.moe_combine(y, plan, chosen, wts, x, E, mo), 10, 3, flush)
+        record(f"moe_combine ({label})", us, nbytes=(rows + 2 * T) * width * 2)
+        # --- the dense products of Llama's feed-forward at the same width, for the experts' products to stand beside
+        inner = llama["intermediate_size"]
+        wg = (torch.randn(2 * inner, width, device=dev) * width ** -0.5).to(bf)
+        a2 = torch.empty(T, inner, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.linear(x, wg, a2, swiglu=True), 5, 3, flush)
+        record(f"gate/up product (SwiGLU) ({label})", us, nbytes=wg.numel() * 2 + T * (width + inner) * 2, flops=4 * T * inner * width)
+        # --- the branch norm beside the pre-norm
+        res = torch.randn(T, width, device=dev)
+        branch = torch.randn(T, width, device=dev).to(bf)
+        nw = torch.ones(width, device=dev)
+        cast = torch.empty(T, width, device=dev, dtype=bf)
+        us = 1e3 * _timed(lambda: K.norm_add(res, branch, nw, 1e-6, cast_out=cast), 10, 3, flush)
+        record(f"norm_add ({label})", us, nbytes=T * width * (2 + 4 + 4 + 2), like="llm_add_rmsnorm")
+        us = 1e3 * _timed(lambda: K.add_rmsnorm(res, branch, nw, 1e-6, cast), 10, 3, flush)
+        record(f"llm_add_rmsnorm ({label})", us, nbytes=T * width * (2 + 4 + 4 + 2))
+    return out
+
 
 def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_source) -> dict:
     import torch
@@ -205,7 +369,8 @@ def run(family, shape, steps, warmup, batch, context, prefill_tokens, peaks_and_
     rows = [_model_runs(f"{family}-{shape}", lif, lif["vocab"], batch, context, steps, warmup, prefill_tokens, flush),
             _model_runs(f"{llama_name} cut to {len(lif['layers'])} layers", llama, llama["vocab_size"], batch, context, steps, warmup,
                         prefill_tokens, flush)]
-    alone = _kernels_alone(lif, llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
+    alone = {"lifusun": _kernels_alone_lifusun, "rodapel": _kernels_alone_rodapel}[family](
+        lif, llama, prefill_tokens, batch, context, peaks["hbm_gbs"], flush)
     return {"family": family, "shape": shape, "dtype": "bf16", "data": "synthetic (random weights, random tokens)",
             "models": rows, "kernels_alone": alone, "copy_bandwidth_gbs": peaks["hbm_gbs"], "peaks": f"of {source}",
             "l2": "256 MB written between timed runs", "steps": steps, "warmup": warmup, "seconds": round(time.time() - t0, 1)}

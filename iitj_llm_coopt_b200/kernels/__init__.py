@@ -110,6 +110,11 @@ _SIGNATURES = {
     "llm_attention_flat": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                            _c_void_p],
+    "llm_attention_flat_mma_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_longlong],
+    "llm_attention_flat_mma_heads_per_block": [_c_int, _c_int],
+    "llm_attention_flat_mma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                               _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                               _c_void_p, _c_void_p, _c_void_p],
     "llm_gemm_grouped_tile_rows": [],
     "llm_gemm_grouped": [_c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p,
                          ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -326,6 +331,7 @@ class Kernels:
         self.decode_tma = os.environ.get("IITJ_DECODE_TMA", "1") != "0"     # decode attention fetches keys and values by TMA
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
+        self.flat_mma = os.environ.get("IITJ_FLAT_MMA", "1") != "0"                     # tensor-core attention over flat pages
         self.talking_mma = os.environ.get("IITJ_TALKING_MMA", "1") != "0"               # tensor-core talking attention for prompt portions
         self.retention_blocks = int(os.environ.get("IITJ_RETENTION_BLOCKS", "0"))        # blocks the retention walk aims at (0: its own rule)
         self.retention_segments = int(os.environ.get("IITJ_RETENTION_SEGMENTS", "0"))    # 1: never in segments, 2: always
@@ -949,8 +955,19 @@ class Kernels:
                    _ptr(cache_layer) if slots is not None else None, _ptr(slots), stride, page_size, DTYPE_CODE[qkv.dtype], tokens,
                    heads, kv_heads, dim, vdim, self._stream())
 
+    def flat_tokens_per_tile(self, heads: int, kv_heads: int) -> int:
+        """Neighbouring tokens of one request that a block of the tensor-core attention over flat pages takes."""
+        return 64 // self.lib.llm_attention_flat_mma_heads_per_block(heads, kv_heads)
+
+    def flat_key_splits(self, requests: int, heads: int, kv_heads: int, value_dim: int, longest: int) -> int:
+        """Over how many blocks the keys of each decoded token are shared out: enough for about two blocks per SM, each with at
+        least eight key tiles of 32."""
+        per = self.lib.llm_attention_flat_mma_heads_per_block(heads, kv_heads)
+        blocks = requests * kv_heads * -(-(heads // kv_heads) // per) * -(-value_dim // (64 if value_dim <= 64 else 128))
+        return max(1, min(32, (2 * self.sm_count) // max(blocks, 1), longest // 256))
+
     def attention_flat(self, q, cache_layer, meta, out, heads, kv_heads, key_dim, value_dim, shared_value: bool = False,
-                       window: int = 0, scale: float = 1.0, gate=None):
+                       window: int = 0, scale: float = 1.0, gate=None, plan=None):
         """Attention of every token's query heads (the leading heads * key_dim numbers of q's rows) over the flat-page
         cache of its request: keys of key_dim, values of value_dim (`shared_value`: the leading value_dim numbers of the key
         rows), a sliding window (0: all earlier keys), optionally each head's output times sigmoid(gate[t, head])."""
@@ -968,6 +985,22 @@ class Kernels:
             _check(gate, "attention_flat.gate", torch.float32, 2)
             _need(tuple(gate.shape) == (tokens, heads), "attention_flat.gate: [tokens, heads]")
         page_size = self._flat_page_size(cache_layer, kv_heads, key_dim, value_dim, shared_value)
+        tiles = plan.device_arrays.get("tiles") if plan is not None else None
+        if tiles is not None and q.dtype == torch.bfloat16 and self.flat_mma and q.shape[1] % 8 == 0 and \
+                self.lib.llm_attention_flat_mma_supported(heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, cache_layer.shape[1]):
+            # prompt portions and decoded tokens alike on the tensor cores (csrc/attention_flat_mma.cu)
+            splits = int(getattr(plan, "splits", 1))
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = self._scratch("flat.part_o", tokens * heads * splits * value_dim, q.device)
+                part_ml = self._scratch("flat.part_ml", tokens * heads * splits * 2, q.device)
+            self._call("llm_attention_flat_mma", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
+                       meta.block_table.shape[1], _ptr(tiles), tiles.shape[0] // 4, _ptr(gate), _ptr(out), out.shape[1], tokens, heads,
+                       kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size, int(window), float(scale), splits,
+                       _ptr(part_o), _ptr(part_ml), self._stream())
+            if splits > 1:
+                self.launches += 1      # the merge kernel
+            return out
         self._call("llm_attention_flat", _ptr(q), q.shape[1], _ptr(cache_layer), cache_layer.shape[1], _ptr(meta.block_table),
                    meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(gate), _ptr(out), out.shape[1],
                    DTYPE_CODE[q.dtype], tokens, heads, kv_heads, key_dim, value_dim, 1 if shared_value else 0, page_size,

@@ -16,6 +16,7 @@ import torch
 
 from ..config.specs import CacheNeed
 from .base import ParamSpec, Part
+from .flat_tiles import flat_prepare_key, plan_flat_tiles
 
 
 class GatedAttention(Part):
@@ -33,6 +34,7 @@ class GatedAttention(Part):
         self.eps = float(spec.option("eps", 1e-6))
         self.cols = self.heads * self.head_dim + self.kv_heads * (self.head_dim + self.value_dim)
         self.qkv = self.o = self.q_norm = self.k_norm = self.gate = None
+        self.prepare_key = flat_prepare_key(self.heads, self.kv_heads, self.head_dim, self.value_dim, self.window)
 
     @classmethod
     def parameters(cls, spec) -> dict:
@@ -51,6 +53,9 @@ class GatedAttention(Part):
     def cache_need(cls, spec) -> CacheNeed:
         return CacheNeed(kind="paged_kv", kv_heads=spec.kv_heads, head_dim=spec.head_dim, window=int(spec.window),
                          value_dim=spec.value_dim or spec.head_dim)
+
+    def prepare_step(self, shape):
+        return plan_flat_tiles(self.k, shape, self.heads, self.kv_heads, self.head_dim, self.value_dim, self.window)
 
     def load(self, tensors: dict) -> None:
         super().load(tensors)
@@ -71,6 +76,6 @@ class GatedAttention(Part):
                               self.heads, self.kv_heads, self.head_dim, self.value_dim)
         attn = ctx.buffer("gattn.ctx", (t, self.heads * self.value_dim), self.dtype)
         self.k.attention_flat(qkv, view, meta, attn, self.heads, self.kv_heads, self.head_dim, self.value_dim,
-                              window=self.window, scale=self.scale, gate=gate)
+                              window=self.window, scale=self.scale, gate=gate, plan=ctx.prepared.get(self.prepare_key))
         out = ctx.buffer("attn.out", (t, self.width), self.dtype)
         return self.k.linear(attn, self.o, out)

@@ -21,6 +21,7 @@ import torch
 
 from ..config.specs import CacheNeed
 from .base import ParamSpec, Part
+from .flat_tiles import flat_prepare_key, plan_flat_tiles
 
 
 class LatentAttention(Part):
@@ -39,6 +40,7 @@ class LatentAttention(Part):
         self.q_width = self.heads * (self.head_dim + self.rot_dim)
         self.row = self.rank + self.rot_dim            # what the cache holds per token, and a head's absorbed query
         self.q_dkv = self.dkv_norm = self.uk = self.uv = self.o = self.uk_t = self.uv_g = None
+        self.prepare_key = flat_prepare_key(self.heads, 1, self.row, self.rank, 0)
 
     @classmethod
     def parameters(cls, spec) -> dict:
@@ -58,6 +60,9 @@ class LatentAttention(Part):
 
     def subparts(self) -> tuple:
         return (self.position,) if self.position is not None else ()
+
+    def prepare_step(self, shape):
+        return plan_flat_tiles(self.k, shape, self.heads, 1, self.row, self.rank, 0)
 
     def load(self, tensors: dict) -> None:
         super().load(tensors)
@@ -80,7 +85,8 @@ class LatentAttention(Part):
                               meta.slots if call.write else None, self.heads, self.head_dim, self.rot_dim, self.rank)
         self.k.linear_by_group(qd, self.uk_t, q, a_stride=self.head_dim + self.rot_dim, out_stride=self.row)
         lat = ctx.buffer("lat.ctx", (t, self.heads * self.rank), self.dtype)
-        self.k.attention_flat(q, view, meta, lat, self.heads, 1, self.row, self.rank, shared_value=True, scale=self.scale)
+        self.k.attention_flat(q, view, meta, lat, self.heads, 1, self.row, self.rank, shared_value=True, scale=self.scale,
+                              plan=ctx.prepared.get(self.prepare_key))
         attn = ctx.buffer("lat.v", (t, self.heads * self.value_dim), self.dtype)
         self.k.linear_by_group(lat, self.uv_g, attn, a_stride=self.rank, out_stride=self.value_dim)
         out = ctx.buffer("attn.out", (t, self.width), self.dtype)

@@ -71,6 +71,33 @@ LIFUSUN_3B = lifusun_shape(3072, 8192, 24, 8, 128, 128256, blocks=2)
 LIFUSUN_1B = lifusun_shape(2048, 8192, 32, 8, 64, 128256, blocks=2)
 LIFUSUN_TOY = lifusun_shape(512, 1408, 8, 2, 64, 4096, blocks=1)
 
+def rodapel_shape(width, inner, heads, kv_heads, head_dim, vocab, blocks, window=4096, kv_rank=512, rot_dim=64, experts=8,
+                  identity=2, top=2, wkv_head=64, decay_rank=64) -> dict:
+    """A Rodapel config.json of `blocks` groups of four layers (windowed attention with a dense feed-forward, then latent
+    attention, wkv and windowed attention with routed ones), with the layer sizes of a Llama of the same width: for runs
+    with random weights beside that Llama.  A routed layer holds `experts` experts of half the dense inner width, of
+    which a token uses `top`: as much arithmetic per token as the dense layer, `experts` / 2 times its weights."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": window}}
+    lat = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank,
+           "scale": (head_dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 1000000.0}}
+    rec = {"heads": width // wkv_head, "dim": wkv_head, "decay_rank": decay_rank}
+    dense = {"kind": "dense", "ff": inner, "limit": 7.0}
+    routed = {"kind": "moe", "expert": {"ff": inner // 2, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top}}
+    layers = []
+    for _ in range(blocks):
+        layers += [{"type": "attention", "mixer": dict(att), "mlp": dict(dense)},
+                   {"type": "latent_attention", "mixer": copy.deepcopy(lat), "mlp": copy.deepcopy(routed)},
+                   {"type": "wkv", "mixer": dict(rec), "mlp": copy.deepcopy(routed)},
+                   {"type": "attention", "mixer": dict(att), "mlp": copy.deepcopy(routed)}]
+    return {"architecture": "Rodapel", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+# Rodapel at the layer sizes of the Llama shapes above (8 layers each)
+RODAPEL_8B = rodapel_shape(4096, 14336, 32, 8, 128, 128256, blocks=2)
+RODAPEL_3B = rodapel_shape(3072, 8192, 24, 8, 128, 128256, blocks=2)
+RODAPEL_1B = rodapel_shape(2048, 8192, 32, 8, 64, 128256, blocks=2)
+RODAPEL_TOY = rodapel_shape(512, 1408, 8, 2, 64, 4096, blocks=1, window=256, kv_rank=128, rot_dim=32, experts=4, identity=1)
+
 # name -> (label used in reports, config.json dict)
 SHAPES = {
     "8b": ("llama-3.1-8b-shape-random", LLAMA_3_1_8B),
@@ -83,6 +110,10 @@ SHAPES = {
     "lifusun-3b": ("lifusun-3b-layers-random", LIFUSUN_3B),
     "lifusun-1b": ("lifusun-1b-layers-random", LIFUSUN_1B),
     "lifusun-toy": ("lifusun-toy-layers-random", LIFUSUN_TOY),
+    "rodapel-8b": ("rodapel-8b-layers-random", RODAPEL_8B),
+    "rodapel-3b": ("rodapel-3b-layers-random", RODAPEL_3B),
+    "rodapel-1b": ("rodapel-1b-layers-random", RODAPEL_1B),
+    "rodapel-toy": ("rodapel-toy-layers-random", RODAPEL_TOY),
 }
 
 

@@ -73,8 +73,10 @@ ROD_D = (config(48, 77, 2e-5, [
 CONFIGS = {"A": (ROD_A, 21, 16), "B": (ROD_B, 22, 8), "C": (ROD_C, 23, 16), "D": (ROD_D, 24, 4)}      # (config, ranks), seed, page size
 
 
-def make_tensors(cfg, ranks, seed, std=0.08):
-    """{checkpoint name: bfloat16 tensor}.  `ranks`: {layer index: rank of a wkv layer's decay projection}."""
+def make_tensors(cfg, ranks, seed, std=0.08, soft=False):
+    """{checkpoint name: bfloat16 tensor}.  `ranks`: {layer index: rank of a wkv layer's decay projection}.  `soft`: decays
+    that depend less steeply on the token (a decay is exp(-exp(x)): where x is large, bfloat16's rounding of the token's row
+    moves the decay by several per cent a token, which compounds in the state)."""
     g = torch.Generator().manual_seed(seed)
 
     def normal(*shape, s=std):
@@ -109,8 +111,8 @@ def make_tensors(cfg, ranks, seed, std=0.08):
             for s in "rkvgw":
                 t[p + "mu." + s] = torch.rand(w, generator=g)
             t[p + "r"], t[p + "k"], t[p + "v"], t[p + "g"] = (normal(n, w, s=0.2) for _ in range(4))
-            t[p + "w1"], t[p + "w2"] = normal(rank, w, s=0.3), normal(n, rank, s=0.8)
-            t[p + "w0"] = normal(n, s=1.0) - 1.5             # decays from almost none to strong
+            t[p + "w1"], t[p + "w2"] = normal(rank, w, s=0.3), normal(n, rank, s=0.2 if soft else 0.8)
+            t[p + "w0"] = normal(n, s=0.5 if soft else 1.0) - (2.5 if soft else 1.5)             # decays from almost none to strong
             t[p + "u"] = normal(m["heads"], m["dim"], s=0.5)
             t[p + "norm"] = gains(n)
             t[p + "o"] = normal(w, n)
@@ -132,10 +134,10 @@ def make_tensors(cfg, ranks, seed, std=0.08):
     return {k: v.to(torch.bfloat16).contiguous() for k, v in t.items()}
 
 
-def write_model(cfg_and_ranks, out_dir, seed, std=0.08, tensors=None):
+def write_model(cfg_and_ranks, out_dir, seed, std=0.08, tensors=None, soft=False):
     cfg, ranks = cfg_and_ranks
     os.makedirs(out_dir, exist_ok=True)
-    save_file(tensors or make_tensors(cfg, ranks, seed, std), os.path.join(out_dir, "model.safetensors"))
+    save_file(tensors or make_tensors(cfg, ranks, seed, std, soft), os.path.join(out_dir, "model.safetensors"))
     with open(os.path.join(out_dir, "config.json"), "w") as f:
         json.dump(cfg, f)
     return out_dir

@@ -140,6 +140,33 @@ def paged(dtype, requests, lens, page, per_token, seed=0):
     return cache.cuda(), table.cuda()
 
 
+def flat_plan(K, token_request, positions, heads, kv_heads, key_dim, value_dim, window, splits=None):
+    """The step plan of the mixers over flat pages (tiles of neighbouring tokens of one request) for the tokens of a test:
+    with it, and bfloat16 sizes it takes, `attention_flat` runs on the tensor cores."""
+    from iitj_llm_coopt_b200.parts.base import StepShape
+    from iitj_llm_coopt_b200.parts.flat_tiles import plan_flat_tiles
+    lens, ends = [], []
+    for i, (b, p) in enumerate(zip(token_request, positions)):
+        if i and token_request[i - 1] == b and positions[i - 1] == p - 1:
+            lens[-1] += 1
+            ends[-1] = p + 1
+        else:
+            lens.append(1)
+            ends.append(p + 1)
+    # runs of one request must carry the request's index: the test's requests are numbered as their first run
+    order = []
+    for i, b in enumerate(token_request):
+        if not i or token_request[i - 1] != b or positions[i - 1] != positions[i] - 1:
+            order.append(b)
+    plan = plan_flat_tiles(K, StepShape(lens, ends, len(token_request), False, False, "cuda"), heads, kv_heads, key_dim, value_dim, window)
+    tiles = torch.tensor(plan.arrays["tiles"], dtype=torch.int32).view(-1, 4)
+    tiles[:, 3] = torch.tensor([order[int(r)] for r in tiles[:, 3]], dtype=torch.int32)
+    plan.bind({"tiles": tiles.reshape(-1).cuda()})
+    if splits is not None:
+        plan.splits = splits
+    return plan
+
+
 def meta_for(table, token_request, positions):
     return types.SimpleNamespace(block_table=table, token_request=torch.tensor(token_request, dtype=torch.int32).cuda(),
                                  positions=torch.tensor(positions, dtype=torch.int32).cuda())
@@ -175,9 +202,11 @@ def test_headnorm_store_and_attention(K, dtype, heads, kv_heads, dim, vdim, wind
         close(a[:, :heads * dim], b_[:, :heads * dim], dtype)
         out = torch.empty(T, heads * vdim, dtype=dtype, device="cuda")
         want = torch.empty(T, heads * vdim, dtype=torch.float32, device="cuda")
-        K.attention_flat(a, cache, meta, out, heads, kv_heads, dim, vdim, window=window, scale=0.3, gate=gate)
         RK.attention_flat(b_, ref_cache, meta, want, heads, kv_heads, dim, vdim, window=window, scale=0.3, gate=gate)
-        close(out, want, dtype)
+        for plan in (None, flat_plan(K, req, pos, heads, kv_heads, dim, vdim, window), flat_plan(K, req, pos, heads, kv_heads, dim, vdim, window, splits=3)):
+            out.fill_(float("nan"))
+            K.attention_flat(a, cache, meta, out, heads, kv_heads, dim, vdim, window=window, scale=0.3, gate=gate, plan=plan)
+            close(out, want, dtype)
     written = ~torch.isnan(ref_cache.float())
     assert torch.equal(written, ~torch.isnan(cache.float()))
     close(cache.float()[written], ref_cache.float()[written], dtype)
@@ -185,7 +214,8 @@ def test_headnorm_store_and_attention(K, dtype, heads, kv_heads, dim, vdim, wind
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dim,rot,rotary,rank,page,interleaved", [(8, 64, 32, 32, 128, 16, True), (3, 20, 12, 8, 36, 8, True),
-                                                                        (1, 8, 6, 6, 10, 4, False), (5, 16, 16, 0, 24, 16, True)])
+                                                                        (1, 8, 6, 6, 10, 4, False), (5, 16, 16, 0, 24, 16, True),
+                                                                        (32, 32, 64, 64, 512, 16, True), (80, 16, 16, 16, 160, 32, True)])
 def test_latent_prepare_and_attention(K, dtype, heads, dim, rot, rotary, rank, page, interleaved):
     lens = [50, 3]
     row = rank + rot
@@ -216,9 +246,11 @@ def test_latent_prepare_and_attention(K, dtype, heads, dim, rot, rotary, rank, p
         meta = meta_for(table, req, pos)
         out = torch.empty(T, heads * rank, dtype=dtype, device="cuda")
         want = torch.empty(T, heads * rank, dtype=torch.float32, device="cuda")
-        K.attention_flat(qa, cache, meta, out, heads, 1, row, rank, shared_value=True, scale=0.2)
         RK.attention_flat(qb, ref_cache, meta, want, heads, 1, row, rank, shared_value=True, scale=0.2)
-        close(out, want, dtype)
+        for plan in (None, flat_plan(K, req, pos, heads, 1, row, rank, 0), flat_plan(K, req, pos, heads, 1, row, rank, 0, splits=2)):
+            out.fill_(float("nan"))
+            K.attention_flat(qa, cache, meta, out, heads, 1, row, rank, shared_value=True, scale=0.2, plan=plan)
+            close(out, want, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -289,8 +321,11 @@ def test_planted_keys_at_the_window_s_edges(K, dtype, window, page, total):
         meta = meta_for(table, [0] * len(rows), rows)
         out = torch.empty(len(rows), heads * vdim, dtype=dtype, device="cuda")
         want = torch.empty(len(rows), heads * vdim, dtype=torch.float32, device="cuda")
-        K.attention_flat(q, cache, meta, out, heads, kv_heads, dim, vdim, window=window, scale=1.0)
         RK.attention_flat(q, cache, meta, want, heads, kv_heads, dim, vdim, window=window, scale=1.0)
-        close(out, want, dtype)
+        for plan in (None, flat_plan(K, [0] * len(rows), rows, heads, kv_heads, dim, vdim, window),
+                     flat_plan(K, [0] * len(rows), rows, heads, kv_heads, dim, vdim, window, splits=4)):
+            out.fill_(float("nan"))
+            K.attention_flat(q, cache, meta, out, heads, kv_heads, dim, vdim, window=window, scale=1.0, plan=plan)
+            close(out, want, dtype)
         if window:
             assert (want[:, :vdim].amax(1) > 1.0).any()       # the planted value shows in the answer

@@ -486,7 +486,7 @@ class TorchKernels:
                 vplane[p, :, o, :] = v[t].to(cache.dtype)
 
     def attention_flat(self, q, cache, meta, out, heads, kv_heads, key_dim, value_dim, shared_value=False, window=0, scale=1.0,
-                       gate=None):
+                       gate=None, plan=None):
         out.copy_(ref_attention_flat(q, None, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
                                      key_dim, value_dim, shared_value, window, scale, gate))
         return out
