@@ -8,7 +8,7 @@
 // stages, one tile ahead of the arithmetic.  Per key tile (tiles start at multiples
 // of 32 of the key position): S = Q K^T by mma.sync m16n8k16 (a warp owns 16 rows), mask and running softmax in float32
 // registers, P rounded to bfloat16 only as the operand of P V, V fragments by ldmatrix.trans from the row-major tile, O in
-// float32 registers.  A value head wider than 128 is cut into slices of 128 over blockIdx.z (each slice's blocks recompute
+// float32 registers.  A value head wider than 256 is cut into slices of 256 over blockIdx.z (each slice's blocks recompute
 // S).  With `splits` > 1 a block walks only its share of the key tiles and leaves (O, m, l) for the merge kernel, so a few
 // decoded tokens over long contexts still fill the GPU.  Rows of a tile that no query of the tile can see are never read
 // from the cache (they may lie in pages a window has given back).
@@ -16,7 +16,10 @@
 
 namespace {
 
-constexpr int kRows = 64, kKeys = 32, kPad = 8, kSlice = 128;
+constexpr int kRows = 64, kKeys = 32, kPad = 8;
+
+// Width of a block's slice of the value head: wider slices recompute the scores less often but hold more of O in registers.
+static inline int slice_width(int value_dim) { return value_dim <= 64 ? 64 : value_dim <= 128 ? 128 : 256; }
 
 struct FlatMmaArgs {
     const __nv_bfloat16* q; int q_stride;
@@ -41,7 +44,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NT>      // n-tiles of 8 value dims a block's slice holds (16: slices of 128, 8: of 64)
+template <int NT>      // n-tiles of 8 value dims a block's slice holds (32: slices of 256, 16: of 128, 8: of 64)
 __global__ void __launch_bounds__(128)
 attention_flat_mma_kernel(const FlatMmaArgs a) {
     pdl_trigger();
@@ -91,6 +94,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         row_pos[e] = pos0 + ti;
         row_lo[e] = a.window > 0 ? max(0, row_pos[e] - a.window + 1) : 0;
     }
+    const bool warp_live = (warp * 16) / hpb < ntok;
     float o[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n)
@@ -140,23 +144,30 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();                                   // this tile has landed for every thread (and Qs is written, first time)
-        // S = Q K^T for the warp's 16 rows and the tile's 32 keys
+        // S = Q K^T for the warp's 16 rows and the tile's 32 keys (a warp whose rows all lie beyond the tile's tokens, as half
+        // of them do for one decoded token of 32 heads, only helps with the copies and the barriers)
+        if (warp_live) {
         float s[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-        const bf16* qrow = Qs + (size_t)(warp * 16 + gq) * ldk + 2 * tq;
+        // fragments by ldmatrix.x4: the left operand's four 8x8 pieces of 16 rows x 16 dims at once, and the right operand's
+        // pieces of two blocks of 8 keys at once (a key tile's rows are the product's columns as they lie)
+        const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(
+            Qs + (size_t)(warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldk + (lane >> 4) * 8);
+        const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(
+            Ks + (size_t)((lane >> 4) * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8);
         for (int ks = 0; ks < kd; ks += 16) {
-            uint32_t fa[4];
-            fa[0] = *reinterpret_cast<const uint32_t*>(qrow + ks);
-            fa[1] = *reinterpret_cast<const uint32_t*>(qrow + 8 * ldk + ks);
-            fa[2] = *reinterpret_cast<const uint32_t*>(qrow + ks + 8);
-            fa[3] = *reinterpret_cast<const uint32_t*>(qrow + 8 * ldk + ks + 8);
+            uint32_t fa[4], fb[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(fa[0]), "=r"(fa[1]), "=r"(fa[2]), "=r"(fa[3]) : "r"(q_addr + ks * 2));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const bf16* krow = Ks + (size_t)(j * 8 + gq) * ldk + ks + 2 * tq;
-                mma16816(s[j], fa, *reinterpret_cast<const uint32_t*>(krow), *reinterpret_cast<const uint32_t*>(krow + 8));
+            for (int jj = 0; jj < 2; ++jj) {
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(fb[0]), "=r"(fb[1]), "=r"(fb[2]), "=r"(fb[3]) : "r"(k_addr + (jj * 16 * ldk + ks) * 2));
+                mma16816(s[2 * jj], fa, fb[0], fb[1]);
+                mma16816(s[2 * jj + 1], fa, fb[2], fb[3]);
             }
         }
         // mask, running softmax (each row's 32 scores sit in the four lanes of a quad)
@@ -215,6 +226,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
                     mma16816(o[n], pa, b0, b1);
                 }
             }
+        }
         }
         __syncthreads();                                   // every warp is done with this stage before it is refilled
     }
@@ -283,7 +295,7 @@ LLM_API int llm_attention_flat_mma_supported(int heads, int kv_heads, int key_di
     if (kv_heads <= 0 || heads % kv_heads) return 0;
     if (key_dim % 16 || value_dim % 8 || key_dim > 1024 || value_dim > 1024 || page_stride % 8) return 0;
     if (shared_value && value_dim > key_dim) return 0;
-    const int slice_w = value_dim <= 64 ? 64 : kSlice;
+    const int slice_w = slice_width(value_dim);
     const size_t smem = ((size_t)(kRows + 2 * kKeys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * kKeys * (slice_w + kPad))) * 2;
     return smem <= 200 * 1024;
 }
@@ -315,7 +327,7 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
     a.heads_per_block = llm_attention_flat_mma_heads_per_block(heads, kv_heads);
     a.tokens_per_tile = kRows / a.heads_per_block;
     const int group = heads / kv_heads, head_blocks = (group + a.heads_per_block - 1) / a.heads_per_block;
-    const int slice_w = value_dim <= 64 ? 64 : kSlice;
+    const int slice_w = slice_width(value_dim);
     const int slices = (value_dim + slice_w - 1) / slice_w;
     const size_t smem = ((size_t)(kRows + 2 * kKeys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * kKeys * (slice_w + kPad))) * 2;
     dim3 grid((unsigned)n_tiles * splits, (unsigned)kv_heads * head_blocks, (unsigned)slices);
@@ -323,9 +335,12 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
     if (slice_w == 64) {
         cudaFuncSetAttribute(attention_flat_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         llm_launch(attention_flat_mma_kernel<8>, grid, 128, smem, stream, a);
-    } else {
+    } else if (slice_w == 128) {
         cudaFuncSetAttribute(attention_flat_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         llm_launch(attention_flat_mma_kernel<16>, grid, 128, smem, stream, a);
+    } else {
+        cudaFuncSetAttribute(attention_flat_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        llm_launch(attention_flat_mma_kernel<32>, grid, 128, smem, stream, a);
     }
     LLM_CHECK_LAUNCH("attention_flat_mma");
     if (splits > 1) {

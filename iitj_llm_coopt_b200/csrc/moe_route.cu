@@ -56,7 +56,7 @@ route_topk_kernel(const float* __restrict__ z, const float* __restrict__ correct
 
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ chosen, int pairs, int top, int experts, int tile_rows, int* __restrict__ source,
-                int* __restrict__ place, int* __restrict__ tiles, int max_tiles) {
+                int* __restrict__ place, int* __restrict__ tiles, int max_tiles, int* __restrict__ counts_out) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ int plan_smem[];          // counts [experts], first rows [experts]
@@ -78,6 +78,7 @@ moe_plan_kernel(const int* __restrict__ chosen, int pairs, int top, int experts,
         int row = 0, n_tiles = 0;
         for (int e = 0; e < experts; ++e) {
             first[e] = row;
+            if (counts_out) counts_out[e] = count[e];
             for (int r = 0; r < count[e]; r += tile_rows) {
                 if (n_tiles < max_tiles) {
                     int* rec = tiles + 4 + 4 * n_tiles;
@@ -125,7 +126,39 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ place, const
     }
 }
 
+// dst[r] = src[index[r]] for r < rows[0] (the count lives on the device), 16 bytes a thread and step when the rows allow it
+template <typename T>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ index, const int* __restrict__ live_rows, T* __restrict__ dst,
+                   int width, int vec) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (r >= live_rows[0]) return;
+    const T* from = src + (size_t)index[r] * width;
+    T* to = dst + (size_t)r * width;
+    if (vec) {
+        const int n = width * (int)sizeof(T) / 16;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<uint4*>(to)[i] = reinterpret_cast<const uint4*>(from)[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = from[i];
+    }
+}
+
 }  // namespace
+
+// dst [max_rows, width] <- src rows by index, for the first live_rows[0] rows (a device count, e.g. tiles + 1 of llm_moe_plan).
+LLM_API int llm_gather_rows(const void* src, const int* index, const int* live_rows, void* dst, int dtype, int max_rows, int width,
+                            cudaStream_t stream) {
+    if (max_rows == 0) return 0;
+    return llm_dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        const int vec = !((width * sizeof(T)) % 16) && !((uintptr_t)src & 15) && !((uintptr_t)dst & 15);
+        llm_launch(gather_rows_kernel<T>, (unsigned)max_rows, 256, 0, stream, (const T*)src, index, live_rows, (T*)dst, width, vec);
+        LLM_CHECK_LAUNCH("gather_rows");
+        return 0;
+    });
+}
 
 LLM_API int llm_route_topk(const float* z, const float* correction, int* chosen, float* weights, int tokens, int outputs, int top,
                            cudaStream_t stream) {
@@ -139,12 +172,13 @@ LLM_API int llm_route_topk(const float* z, const float* correction, int* chosen,
 }
 
 // tiles: int32 [(max_tiles + 1) * 4]: the first four ints are (count, sorted rows, 0, 0), then one record per tile.
+// counts: null, or int32 [experts] that receives every expert's row count (for a caller that wants them on the host).
 LLM_API int llm_moe_plan(const int* chosen, int pairs, int top, int experts, int tile_rows, int* source, int* place, int* tiles,
-                         int max_tiles, cudaStream_t stream) {
+                         int max_tiles, int* counts, cudaStream_t stream) {
     if (pairs == 0) return 0;
     if (experts <= 0 || experts > 4096) LLM_FAIL(-1, "moe_plan: %d experts (1 to 4096)", experts);
     llm_launch(moe_plan_kernel, 1, 1024, (size_t)2 * experts * sizeof(int), stream, chosen, pairs, top, experts, tile_rows, source,
-               place, tiles, max_tiles);
+               place, tiles, max_tiles, counts);
     LLM_CHECK_LAUNCH("moe_plan");
     return 0;
 }

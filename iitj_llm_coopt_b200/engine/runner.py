@@ -321,7 +321,7 @@ class ModelRunner:
                           first_portion=dev("first_portion"), groups=metas, cache=cache,
                           workspace=self.workspace, requests=[e.request for e in entries] + [None] * pad,
                           query_lens=qlens, starts=starts, slots_host=slots_b, prepared=prepared)
-        if graphable:
+        if graphable and all(getattr(p, "capture", True) for p in prepared.values()):
             form = ("decode", B) if decode_shaped else (tuple(qlens), tuple(len(e.want) for e in entries))
             key = (form, tuple(sorted(widths.items())), fed, tuple((k, p.graph_key) for k, p in prepared.items()))
             logits = self._forward_graphed(key, ctx, eager_runs=self.graph_after if decode_shaped else max(4, self.graph_after))

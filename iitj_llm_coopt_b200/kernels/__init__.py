@@ -120,7 +120,8 @@ _SIGNATURES = {
                          ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_int,
                          _c_void_p, _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "llm_route_topk": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
-    "llm_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
+    "llm_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "llm_gather_rows": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "llm_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                         _c_void_p],
     "llm_token_shift": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
@@ -851,7 +852,12 @@ class Kernels:
         """The most row tiles `moe_plan` can make of `rows` (token, choice) pairs over `experts` experts."""
         return -(-rows // self.lib.llm_gemm_grouped_tile_rows()) + experts
 
-    def moe_plan(self, chosen, experts: int, source, place, tiles):
+    # (token, choice) pairs from which a step's expert products run expert by expert on the dense product kernels
+    # (IITJ_MOE_DENSE_ROWS; 0: never).  Measured at 8B layer sizes, 2,048 tokens of 2 choices over 8 experts: the grouped
+    # kernel's mma.sync tiles reach 150 to 190 TFLOP/s, the dense products 1,000 and more.
+    moe_dense_rows = int(os.environ.get("IITJ_MOE_DENSE_ROWS", "2048"))
+
+    def moe_plan(self, chosen, experts: int, source, place, tiles, counts=None):
         """Sorts the (token, choice) pairs of `chosen` [T, top] by expert on the device: source [T * top] (token of each
         sorted row), place [T * top] (sorted row of each pair, -1 for a choice >= experts), tiles [bound + 1, 4] (count in
         front, then (expert, first row, rows) records).  Returns what `moe_linear` and `moe_combine` take as `plan`."""
@@ -862,9 +868,21 @@ class Kernels:
         _check(tiles, "moe_plan.tiles", torch.int32, 2)
         bound = self.moe_tile_bound(chosen.numel(), experts)
         _need(tiles.shape[1] == 4 and tiles.shape[0] >= bound + 1, "moe_plan.tiles: [tile bound + 1, 4]")
+        if counts is not None:
+            _check(counts, "moe_plan.counts", torch.int32, 1)
+            _need(counts.shape[0] >= experts, "moe_plan.counts: one per expert")
         self._call("llm_moe_plan", _ptr(chosen), chosen.numel(), chosen.shape[1], int(experts),
-                   self.lib.llm_gemm_grouped_tile_rows(), _ptr(source), _ptr(place), _ptr(tiles), bound, self._stream())
-        return {"source": source, "place": place, "tiles": tiles, "bound": bound}
+                   self.lib.llm_gemm_grouped_tile_rows(), _ptr(source), _ptr(place), _ptr(tiles), bound, _ptr(counts), self._stream())
+        return {"source": source, "place": place, "tiles": tiles, "bound": bound, "counts": counts}
+
+    def gather_rows(self, x, plan, out):
+        """out[r] = x[plan source of r] for every sorted row r of `plan` (`moe_plan`): the experts' rows side by side."""
+        _check(x, "gather_rows.x", tuple(DTYPE_CODE), 2)
+        _check(out, "gather_rows.out", x.dtype, 2)
+        _need(out.shape[1] == x.shape[1] and out.shape[0] == plan["source"].shape[0], "gather_rows: shapes do not fit")
+        self._call("llm_gather_rows", _ptr(x), _ptr(plan["source"]), plan["tiles"].data_ptr() + 4, _ptr(out), DTYPE_CODE[x.dtype],
+                   out.shape[0], x.shape[1], self._stream())
+        return out
 
     def moe_linear(self, a, w, out, plan, gather: bool = False, glu: bool = False, limit: float = 0.0, slope: float = 1.0):
         """out[r] = a[row of r] . w[expert of r]^T for every sorted row r of `plan`; with `gather` a's rows are tokens
@@ -963,7 +981,7 @@ class Kernels:
         """Over how many blocks the keys of each decoded token are shared out: enough for about two blocks per SM, each with at
         least eight key tiles of 32."""
         per = self.lib.llm_attention_flat_mma_heads_per_block(heads, kv_heads)
-        blocks = requests * kv_heads * -(-(heads // kv_heads) // per) * -(-value_dim // (64 if value_dim <= 64 else 128))
+        blocks = requests * kv_heads * -(-(heads // kv_heads) // per) * -(-value_dim // (64 if value_dim <= 64 else 128 if value_dim <= 128 else 256))
         return max(1, min(32, (2 * self.sm_count) // max(blocks, 1), longest // 256))
 
     def attention_flat(self, q, cache_layer, meta, out, heads, kv_heads, key_dim, value_dim, shared_value: bool = False,

@@ -26,7 +26,8 @@ it is called on the host once per step (once for all parts that share a `prepare
 the step's `StepShape`; the int32 arrays it returns travel in the same buffer, come back to it as device views
 through `StepPlan.bind`, and its forward finds the plan in `ctx.prepared[prepare_key]`.  Whatever of the plan a
 captured CUDA graph freezes (a launch shape, a split count) goes into `StepPlan.graph_key`, so a step with another
-value is captured anew.
+value is captured anew.  A plan with `capture = False` keeps its step out of CUDA graphs altogether (a part that reads
+something back on the host for steps of that shape).
 
 A delta (and the qkv handed to a position encoding) may be a `kernels.PartialSums`: a matrix product
 that was split along k and whose parts are still to be added.  It is only handed to a norm or a position
@@ -63,6 +64,8 @@ class StepPlan:
     """A part's own per-step index arrays: `arrays` {name: int32 numpy array or list} go into the step's one
     staging buffer; `graph_key` is what a captured graph of this step freezes; `bind(views)` receives the arrays
     as device tensors (same names) after the copy was issued."""
+
+    capture = True       # False: a step with this plan is never captured into, or replayed from, a CUDA graph
 
     def __init__(self, arrays: dict | None = None, graph_key=()):
         self.arrays, self.graph_key = arrays or {}, graph_key

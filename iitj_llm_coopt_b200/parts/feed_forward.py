@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import ParamSpec, Part
+from .base import ParamSpec, Part, StepPlan
 
 
 class SwiGLU(Part):
@@ -75,7 +75,10 @@ class RoutedGLU(Part):
     The last `identity` router outputs stand for experts without tensors that hand their input back (s[e] * x).
     Rows are sorted by expert on the device (`Kernels.moe_plan`), the experts' products run as one grouped product each
     (the first reads its rows through the sorted index, applies the gate in its epilogue), and the chosen experts'
-    outputs of a token are added in the order of its choices, so a token's result does not depend on the batch."""
+    outputs of a token are added in the order of its choices, so a token's result does not depend on the batch.
+    Nothing of that comes back to the host, so decode steps replay from CUDA graphs.  A step with many rows (a prompt
+    portion; `Kernels.moe_dense_rows`) that is not being captured reads the experts' row counts once and runs each
+    expert's rows, gathered side by side, through the dense product kernels, which are several times faster at that size."""
     graph_safe = True
 
     def __init__(self, spec, kernels, dtype):
@@ -85,6 +88,20 @@ class RoutedGLU(Part):
         self.identity = int(spec.option("identity", 0))
         self.limit, self.slope = float(spec.option("limit", 0.0)), float(spec.option("slope", 1.0))
         self.router = self.correction = self.expert_gate_up = self.expert_down = None
+        self.prepare_key = f"routed_glu.{self.top}"          # layers with as many choices a token share the step's plan
+
+    def _by_expert(self, tokens: int) -> bool:
+        """Whether a step of `tokens` tokens runs its experts one by one on the dense product kernels."""
+        dense_rows = getattr(self.k, "moe_dense_rows", 0)
+        return bool(self.experts) and bool(dense_rows) and tokens * self.top >= dense_rows
+
+    def prepare_step(self, shape):
+        """A step that reads the experts' row counts on the host stays out of CUDA graphs."""
+        if not self._by_expert(shape.num_tokens):
+            return None
+        plan = StepPlan()
+        plan.capture = False
+        return plan
 
     @classmethod
     def parameters(cls, spec) -> dict:
@@ -112,12 +129,33 @@ class RoutedGLU(Part):
         plan = y = None
         if self.experts:
             rows = t * self.top
+            w1 = self.expert_gate_up.view(self.experts, 2 * self.inner, self.width)
+            w2 = self.expert_down.view(self.experts, self.width, self.inner)
+            by_expert = self._by_expert(t) and not (x.is_cuda and torch.cuda.is_current_stream_capturing())
+            counts = ctx.buffer("moe.counts", (self.experts,), torch.int32) if by_expert else None
             plan = self.k.moe_plan(chosen, self.experts, ctx.buffer("moe.source", (rows,), torch.int32),
                                    ctx.buffer("moe.place", (rows,), torch.int32),
-                                   ctx.buffer("moe.tiles", (self.k.moe_tile_bound(rows, self.experts) + 1, 4), torch.int32))
-            act = ctx.buffer("moe.act", (t * self.top, self.inner), self.dtype)
-            self.k.moe_linear(x, self.expert_gate_up.view(self.experts, 2 * self.inner, self.width), act, plan, gather=True,
-                              glu=True, limit=self.limit, slope=self.slope)
-            y = ctx.buffer("moe.y", (t * self.top, self.width), self.dtype)
-            self.k.moe_linear(act, self.expert_down.view(self.experts, self.width, self.inner), y, plan)
+                                   ctx.buffer("moe.tiles", (self.k.moe_tile_bound(rows, self.experts) + 1, 4), torch.int32),
+                                   **({"counts": counts} if by_expert else {}))
+            act = ctx.buffer("moe.act", (rows, self.inner), self.dtype)
+            y = ctx.buffer("moe.y", (rows, self.width), self.dtype)
+            if by_expert:
+                sizes = counts.tolist()                      # the one read of the host in this layer
+                xs = self.k.gather_rows(x, plan, ctx.buffer("moe.rows", (rows, self.width), self.dtype))
+                gu = ctx.buffer("moe.gate_up", (rows, 2 * self.inner), self.dtype)
+                live, spans = 0, []
+                for n in sizes:
+                    spans.append((live, live + n))
+                    live += n
+                for e, (lo, hi) in enumerate(spans):
+                    if hi > lo:
+                        self.k.linear(xs[lo:hi], w1[e], gu[lo:hi])
+                if live:
+                    self.k.glu_clamped(gu[:live], act[:live], self.limit, self.slope)
+                for e, (lo, hi) in enumerate(spans):
+                    if hi > lo:
+                        self.k.linear(act[lo:hi], w2[e], y[lo:hi])
+            else:
+                self.k.moe_linear(x, w1, act, plan, gather=True, glu=True, limit=self.limit, slope=self.slope)
+                self.k.moe_linear(act, w2, y, plan)
         return self.k.moe_combine(y, plan, chosen, weights, x, self.experts, out)

@@ -111,6 +111,15 @@ def moe_case(K, dtype, tokens, top, experts, identity, width, ff, chosen=None, s
     assert torch.equal(pk["source"][:n], pr["source"][:n])
     assert int(pk["tiles"][0, 0]) == int(pr["tiles"][0, 0]) and int(pk["tiles"][0, 1]) == n
     close(ok, orf, dtype)
+    # the experts' row counts for a caller that wants them on the host, and the rows gathered side by side
+    rows = tokens * top
+    counts = torch.full((experts,), -1, dtype=torch.int32, device="cuda")
+    plan = K.moe_plan(chosen, experts, torch.zeros(rows, dtype=torch.int32, device="cuda"), torch.zeros(rows, dtype=torch.int32, device="cuda"),
+                      torch.zeros(K.moe_tile_bound(rows, experts) + 1, 4, dtype=torch.int32, device="cuda"), counts=counts)
+    assert counts.tolist() == [int((chosen == e).sum()) for e in range(experts)]
+    side = torch.full((rows, width), 7.0, dtype=dtype, device="cuda")
+    K.gather_rows(x, plan, side)
+    assert torch.equal(side[:n], x[plan["source"][:n].long()]) and (side[n:] == 7.0).all()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -499,7 +499,7 @@ class TorchKernels:
     def moe_tile_bound(self, rows, experts):
         return -(-rows // self.MOE_TILE_ROWS) + experts
 
-    def moe_plan(self, chosen, experts, source, place, tiles):
+    def moe_plan(self, chosen, experts, source, place, tiles, counts=None):
         """Rows (token, choice) sorted by expert: source[r] = token of sorted row r, place[token * top + j] = its sorted row
         (-1 for an expert without tensors), tiles[0, 0] = count, tiles[1 + i] = (expert, first row, rows, 0)."""
         top = chosen.shape[1]
@@ -515,11 +515,22 @@ class TorchKernels:
             for s in range(0, n, self.MOE_TILE_ROWS):
                 recs.append((e, start + s, min(self.MOE_TILE_ROWS, n - s), 0))
             start += n
+        if counts is not None:
+            for e in range(experts):
+                counts[e] = sum(1 for x, _ in order if x == e)
         tiles.zero_()
         tiles[0, 0] = len(recs)
+        tiles[0, 1] = len(order)
         for i, rec in enumerate(recs):
             tiles[1 + i] = torch.tensor(rec, dtype=torch.int32)
-        return {"source": source, "place": place, "tiles": tiles, "rows": len(order)}
+        return {"source": source, "place": place, "tiles": tiles, "rows": len(order), "counts": counts}
+
+    moe_dense_rows = 40          # small, so that the CPU tests take the expert-by-expert way for their longer portions
+
+    def gather_rows(self, x, plan, out):
+        n = plan["rows"]
+        out[:n] = x[plan["source"][:n].long()]
+        return out
 
     def moe_linear(self, a, w, out, plan, gather=False, glu=False, limit=0.0, slope=1.0):
         tiles = plan["tiles"]
