@@ -300,6 +300,12 @@ LLM_API int llm_attention_flat_mma_supported(int heads, int kv_heads, int key_di
     return smem <= 200 * 1024;
 }
 
+// Shared memory of one block in bytes (what bounds the blocks an SM holds at wide rows).
+LLM_API int llm_attention_flat_mma_smem(int key_dim, int value_dim, int shared_value) {
+    const int slice_w = slice_width(value_dim);
+    return (int)(((size_t)(kRows + 2 * kKeys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * kKeys * (slice_w + kPad))) * 2);
+}
+
 // Heads of a group that one block takes (the rest of its 64 rows are neighbouring tokens).
 LLM_API int llm_attention_flat_mma_heads_per_block(int heads, int kv_heads) {
     const int group = heads / (kv_heads > 0 ? kv_heads : 1);

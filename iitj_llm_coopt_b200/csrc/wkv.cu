@@ -58,7 +58,8 @@ template <typename T, int DMAX>
 __global__ void __launch_bounds__(DMAX * 4)
 wkv_scan_kernel(const T* __restrict__ rkvg, const float* __restrict__ decay, const float* __restrict__ u, const float* __restrict__ gain,
                 float eps, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
-                T* __restrict__ out, int heads, int dim, int write, const T* __restrict__ x, float* __restrict__ before, int width) {
+                T* __restrict__ out, int tokens, int heads, int dim, int write, const T* __restrict__ x, float* __restrict__ before,
+                int width) {
     pdl_trigger();
     pdl_wait();
     // Four threads share a column j of S: thread (j, p) keeps the rows 16 q + 4 p + (0..3), q = 0 .. DMAX / 16 - 1, so the four
@@ -92,11 +93,11 @@ wkv_scan_kernel(const T* __restrict__ rkvg, const float* __restrict__ decay, con
         for (int e = 0; e < PER; ++e) {
             const int idx = tid + e * THREADS, c = idx / DMAX, i = idx % DMAX;
             const bool live = c < cnt && i < dim;
-            const size_t row = (size_t)(t0 + c) * 4 * n + (size_t)h * dim + i;
+            const size_t row = (size_t)(t0 + c) * n + (size_t)h * dim + i, stream = (size_t)tokens * n;
             lr[e] = live ? to_f32(rkvg[row]) : 0.f;
-            lk[e] = live ? to_f32(rkvg[row + n]) : 0.f;
-            lv[e] = live ? to_f32(rkvg[row + 2 * n]) : 0.f;
-            lg[e] = live ? to_f32(rkvg[row + 3 * n]) : 0.f;
+            lk[e] = live ? to_f32(rkvg[row + stream]) : 0.f;
+            lv[e] = live ? to_f32(rkvg[row + 2 * stream]) : 0.f;
+            lg[e] = live ? to_f32(rkvg[row + 3 * stream]) : 0.f;
             lw[e] = live ? decay[(size_t)(t0 + c) * n + (size_t)h * dim + i] : 0.f;
         }
     };
@@ -178,11 +179,11 @@ LLM_API int llm_wkv_decay(const float* low, const float* w2, const float* w0, fl
     return 0;
 }
 
-// rkvg [tokens, 4 * heads * dim] of `dtype` (r, k, v, g column blocks); decay [tokens, heads * dim] float32; state
+// rkvg [4 * tokens, heads * dim] of `dtype` (the rows of r, then of k, v and g); decay [tokens, heads * dim] float32; state
 // [slots, heads, dim, dim] float32.  x [tokens, width] and before [slots, width] (or null): the shifted-in row to leave behind.
 LLM_API int llm_wkv_scan(const void* rkvg, const float* decay, const float* u, const float* gain, float eps, float* state,
-                         const int* state_slots, const int* cu_seqlens, void* out, int dtype, int requests, int heads, int dim,
-                         int write, const void* x, float* before, int width, cudaStream_t stream) {
+                         const int* state_slots, const int* cu_seqlens, void* out, int dtype, int tokens, int requests, int heads,
+                         int dim, int write, const void* x, float* before, int width, cudaStream_t stream) {
     if (requests == 0) return 0;
     if (dim <= 0 || dim > 128) LLM_FAIL(-1, "wkv_scan: head size %d must be in [1, 128]", dim);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
@@ -190,7 +191,7 @@ LLM_API int llm_wkv_scan(const void* rkvg, const float* decay, const float* u, c
         const unsigned blocks = (unsigned)requests * heads;
 #define LLM_WKV_CASE(DMAX)                                                                                                   \
         llm_launch(wkv_scan_kernel<T, DMAX>, blocks, DMAX * 4, 0, stream, (const T*)rkvg, decay, u, gain, eps, state, state_slots,   \
-                   cu_seqlens, (T*)out, heads, dim, write, (const T*)x, before, width)
+                   cu_seqlens, (T*)out, tokens, heads, dim, write, (const T*)x, before, width)
         if (dim <= 32) LLM_WKV_CASE(32);
         else if (dim <= 64) LLM_WKV_CASE(64);
         else LLM_WKV_CASE(128);

@@ -234,9 +234,9 @@ def _kernels_alone_rodapel(cfg, llama, tokens, batch, context, hbm_gbs, flush):
         from .parts.base import StepShape
         from .parts.flat_tiles import plan_flat_tiles
 
-        def plan_for(heads, kv_heads, key_dim, value_dim, win):
+        def plan_for(heads, kv_heads, key_dim, value_dim, win, shared=False):
             plan = plan_flat_tiles(K, StepShape([per] * B, [ctx_len] * B, T, label == "decode", False, dev), heads, kv_heads,
-                                   key_dim, value_dim, win)
+                                   key_dim, value_dim, win, shared_value=shared)
             plan.bind({"tiles": i32(plan.arrays["tiles"])})
             return plan
         seen = sum(min(p + 1, window) for p in pos)                     # keys the windowed queries see, in all
@@ -285,7 +285,7 @@ def _kernels_alone_rodapel(cfg, llama, tokens, batch, context, hbm_gbs, flush):
         record(f"absorbed queries, a product per head ({label})", us, nbytes=(T * LH * (LD + LC) + LH * LC * LD) * 2,
                flops=2 * T * LH * LD * LC)
         lo2 = torch.empty(T, LH * LC, device=dev, dtype=bf)
-        lplan = plan_for(LH, 1, row, LC, 0)
+        lplan = plan_for(LH, 1, row, LC, 0, shared=True)
         us = 1e3 * _timed(lambda: K.attention_flat(qa, lat_cache, meta, lo2, LH, 1, row, LC, shared_value=True, scale=0.07, plan=lplan), 3, 3, flush)
         if label == "decode":
             record(f"attention_flat, latent rows ({label})", us, nbytes=B * ctx_len * row * 2, like="llama attention")
@@ -301,7 +301,7 @@ def _kernels_alone_rodapel(cfg, llama, tokens, batch, context, hbm_gbs, flush):
         mixes = torch.empty(5 * T, width, device=dev, dtype=bf)
         us = 1e3 * _timed(lambda: K.token_shift(x, mu, before, ss, tr, cs, mixes), 10, 3, flush)
         record(f"token_shift ({label})", us, nbytes=T * width * 2 * 6)
-        rkvg = torch.randn(T, 4 * n, device=dev).to(bf)
+        rkvg = torch.randn(4 * T, n, device=dev).to(bf)
         decay = torch.rand(T, n, device=dev) * 0.5 + 0.5
         u, g1 = torch.randn(RH, RD, device=dev) * 0.3, torch.ones(n, device=dev)
         state = torch.zeros(B + 1, RH, RD, RD, device=dev)

@@ -112,6 +112,7 @@ _SIGNATURES = {
                            _c_void_p],
     "llm_attention_flat_mma_supported": [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_longlong],
     "llm_attention_flat_mma_heads_per_block": [_c_int, _c_int],
+    "llm_attention_flat_mma_smem": [_c_int, _c_int, _c_int],
     "llm_attention_flat_mma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                                _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                _c_void_p, _c_void_p, _c_void_p],
@@ -128,7 +129,7 @@ _SIGNATURES = {
                         _c_void_p],
     "llm_wkv_decay": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "llm_wkv_scan": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
-                     _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p],
+                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p],
 }
 
 # The library's health words in the order llm_sample copies them out (csrc/common.cuh): which kernel, and what its codes mean.
@@ -977,12 +978,15 @@ class Kernels:
         """Neighbouring tokens of one request that a block of the tensor-core attention over flat pages takes."""
         return 64 // self.lib.llm_attention_flat_mma_heads_per_block(heads, kv_heads)
 
-    def flat_key_splits(self, requests: int, heads: int, kv_heads: int, value_dim: int, longest: int) -> int:
-        """Over how many blocks the keys of each decoded token are shared out: enough for about two blocks per SM, each with at
-        least eight key tiles of 32."""
+    def flat_key_splits(self, requests: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, shared_value: bool,
+                        longest: int) -> int:
+        """Over how many blocks the keys of each decoded token are shared out: as many as fill the SMs once with the blocks an
+        SM holds (two, or one where a block's shared memory leaves no room for a second), each with at least eight key tiles
+        of 32."""
         per = self.lib.llm_attention_flat_mma_heads_per_block(heads, kv_heads)
         blocks = requests * kv_heads * -(-(heads // kv_heads) // per) * -(-value_dim // (64 if value_dim <= 64 else 128 if value_dim <= 128 else 256))
-        return max(1, min(32, (2 * self.sm_count) // max(blocks, 1), longest // 256))
+        resident = max(1, min(2, (227 * 1024) // max(self.lib.llm_attention_flat_mma_smem(key_dim, value_dim, 1 if shared_value else 0), 1)))
+        return max(1, min(32, (resident * self.sm_count) // max(blocks, 1), longest // 256))
 
     def attention_flat(self, q, cache_layer, meta, out, heads, kv_heads, key_dim, value_dim, shared_value: bool = False,
                        window: int = 0, scale: float = 1.0, gate=None, plan=None):
@@ -1054,7 +1058,7 @@ class Kernels:
 
     def wkv_scan(self, rkvg, decay, u, gain, eps, state, state_slots, cu_seqlens, out, heads, dim, write: bool = True,
                  last_rows=None):
-        """The wkv walk with head norm, gain and gate (csrc/wkv.cu): rkvg [T, 4 * heads * dim] (r, k, v, g blocks), decay
+        """The wkv walk with head norm, gain and gate (csrc/wkv.cu): rkvg [4 * T, heads * dim] (the rows of r, then k, v, g), decay
         [T, heads * dim] float32, u [heads, dim], gain [heads * dim], state [slots, heads, dim, dim] float32 (read, and with
         `write` left at the step's last token).  last_rows = (x [T, width], before [slots, width]): each request's last row of
         x becomes its row in `before`."""
@@ -1062,8 +1066,8 @@ class Kernels:
         _check(out, "wkv_scan.out", rkvg.dtype, 2)
         for name, t, d in (("decay", decay, 2), ("u", u, 2), ("gain", gain, 1), ("state", state, 4)):
             _check(t, "wkv_scan." + name, torch.float32, d)
-        tokens, n = rkvg.shape[0], heads * dim
-        _need(rkvg.shape[1] == 4 * n and tuple(decay.shape) == (tokens, n) and tuple(out.shape) == (tokens, n) and
+        tokens, n = rkvg.shape[0] // 4, heads * dim
+        _need(tuple(rkvg.shape) == (4 * tokens, n) and tuple(decay.shape) == (tokens, n) and tuple(out.shape) == (tokens, n) and
               tuple(u.shape) == (heads, dim) and gain.shape[0] == n and tuple(state.shape[1:]) == (heads, dim, dim),
               "wkv_scan: shapes do not fit")
         _check(state_slots, "wkv_scan.state_slots", torch.int32, 1)
@@ -1078,7 +1082,7 @@ class Kernels:
             width = x.shape[1]
             _need(x.shape[0] == tokens and before.shape[1] == width, "wkv_scan.last_rows: shapes do not fit")
         self._call("llm_wkv_scan", _ptr(rkvg), _ptr(decay), _ptr(u), _ptr(gain), float(eps), _ptr(state), _ptr(state_slots),
-                   _ptr(cu_seqlens), _ptr(out), DTYPE_CODE[rkvg.dtype], state_slots.shape[0], heads, dim, 1 if write else 0,
+                   _ptr(cu_seqlens), _ptr(out), DTYPE_CODE[rkvg.dtype], tokens, state_slots.shape[0], heads, dim, 1 if write else 0,
                    _ptr(x), _ptr(before), width, self._stream())
         return out
 

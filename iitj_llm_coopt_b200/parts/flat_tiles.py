@@ -12,7 +12,7 @@ def flat_prepare_key(heads, kv_heads, key_dim, value_dim, window) -> str:
     return f"flat_attention.{heads}.{kv_heads}.{key_dim}.{value_dim}.{window}"
 
 
-def plan_flat_tiles(kernels, shape, heads, kv_heads, key_dim, value_dim, window):
+def plan_flat_tiles(kernels, shape, heads, kv_heads, key_dim, value_dim, window, shared_value=False):
     """StepPlan with `tiles` (first token row, tokens, position of the first, request) and `.splits`, or None when the
     kernel set plans nothing (it then walks a row per warp)."""
     per_tile = getattr(kernels, "flat_tokens_per_tile", None)
@@ -29,7 +29,8 @@ def plan_flat_tiles(kernels, shape, heads, kv_heads, key_dim, value_dim, window)
     if shape.num_tokens == len(shape.query_lens):
         # single decoded tokens: few blocks, long key ranges.  The longest range is rounded up to 512 keys, so that a captured
         # graph (which freezes the count) serves the steps while contexts grow.
-        splits = kernels.flat_key_splits(len(shape.query_lens), heads, kv_heads, value_dim, -(-longest // 512) * 512)
+        splits = kernels.flat_key_splits(len(shape.query_lens), heads, kv_heads, key_dim, value_dim, shared_value,
+                                         -(-longest // 512) * 512)
     plan = StepPlan(arrays={"tiles": tiles}, graph_key=(splits,))
     plan.splits = splits
     return plan

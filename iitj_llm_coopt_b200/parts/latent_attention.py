@@ -62,7 +62,7 @@ class LatentAttention(Part):
         return (self.position,) if self.position is not None else ()
 
     def prepare_step(self, shape):
-        return plan_flat_tiles(self.k, shape, self.heads, 1, self.row, self.rank, 0)
+        return plan_flat_tiles(self.k, shape, self.heads, 1, self.row, self.rank, 0, shared_value=True)
 
     def load(self, tensors: dict) -> None:
         super().load(tensors)

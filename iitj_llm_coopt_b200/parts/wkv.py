@@ -66,9 +66,9 @@ class WKV(Part):
         _, before = ctx.cache.view(call.state)
         mixes = ctx.buffer("wkv.mixes", (len(STREAMS) * t, self.width), self.dtype)
         self.k.token_shift(x, self.mu, before, ctx.state_slots, ctx.token_request, ctx.cu_seqlens, mixes)
-        rkvg = ctx.buffer("wkv.rkvg", (t, 4 * self.inner), self.dtype)
-        self.k.linear_by_group(mixes, self.rkvg.view(4, self.inner, self.width), rkvg, a_stride=t * self.width,
-                               out_stride=self.inner)
+        rkvg = ctx.buffer("wkv.rkvg", (4 * t, self.inner), self.dtype)        # the rows of r, then of k, v and g
+        for s in range(4):
+            self.k.linear(mixes[s * t:(s + 1) * t], self.rkvg[s * self.inner:(s + 1) * self.inner], rkvg[s * t:(s + 1) * t])
         low = ctx.buffer("wkv.low", (t, self.rank), torch.float32)
         self.k.linear(mixes[4 * t:], self.w1, low)
         decay = ctx.buffer("wkv.decay", (t, self.inner), torch.float32)

@@ -288,7 +288,7 @@ def test_wkv(K, dtype, heads, dim, width, rank):
         K.wkv_decay(low, w2, w0, decay[0])
         RK.wkv_decay(low, w2, w0, decay[1])
         close(decay[0], decay[1], torch.float32, scale=1.0)
-        rkvg = rnd(T, 4 * n, dtype=dtype, seed=40 + step)
+        rkvg = rnd(4 * T, n, dtype=dtype, seed=40 + step)
         outs = [torch.empty(T, n, dtype=dtype, device="cuda"), torch.empty(T, n, dtype=torch.float32, device="cuda")]
         K.wkv_scan(rkvg, decay[1], u, gain, 1e-5, states[0], slots, cu, outs[0], heads, dim, last_rows=(x, befores[0]))
         RK.wkv_scan(rkvg, decay[1], u, gain, 1e-5, states[1], slots, cu, outs[1], heads, dim, last_rows=(x, befores[1]))

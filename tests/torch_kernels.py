@@ -305,12 +305,13 @@ def ref_wkv_decay(low, w2, w0):
 
 
 def ref_wkv_scan(rkvg, decay, u, gain, eps, state, state_slots, cu_seqlens, heads, dim):
-    """rkvg [T, 4 * H * D]; state [slots, H, D (key), D (value)] float32.  Returns (gated output [T, H * D], {slot: new state})."""
-    T = rkvg.shape[0]
+    """rkvg [4 * T, H * D] (rows of r, then k, v, g); state [slots, H, D (key), D (value)] float32.  Returns (gated output
+    [T, H * D], {slot: new state})."""
+    T = rkvg.shape[0] // 4
     n = heads * dim
     x = rkvg.float()
-    r, k, v = (x[:, i * n:(i + 1) * n].view(T, heads, dim) for i in range(3))
-    g = torch.nn.functional.silu(x[:, 3 * n:])
+    r, k, v = (x[i * T:(i + 1) * T].view(T, heads, dim) for i in range(3))
+    g = torch.nn.functional.silu(x[3 * T:])
     w = decay.float().view(T, heads, dim)
     o = torch.zeros(T, heads, dim, dtype=torch.float32, device=rkvg.device)
     new = {}
