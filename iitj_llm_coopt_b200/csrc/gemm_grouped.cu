@@ -179,6 +179,113 @@ grouped_bf16_kernel(const GroupedArgs a) {
             }
 }
 
+// The same product with its operands streamed by cp.async through a ring of stages (k-blocks of 64): what the experts' products of
+// a decode step need, where a tile's few rows meet 64 weight rows of the whole k range and the kernel is bound by how many
+// bytes it keeps in flight.  Taken when every 16-byte piece is aligned (else the kernel above runs).
+constexpr int BKP = 64, PADP = 8, STAGES = 3;
+
+template <bool GLU>
+__global__ void __launch_bounds__(128)
+grouped_bf16_pipe_kernel(const GroupedArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    using bf16 = __nv_bfloat16;
+    constexpr int LD = BKP + PADP, NW = GLU ? 2 : 1;
+    extern __shared__ __align__(16) unsigned char grouped_smem[];
+    bf16* As = reinterpret_cast<bf16*>(grouped_smem);                      // [STAGES][BM][LD]
+    bf16* Ws = As + (size_t)STAGES * BM * LD;                              // [STAGES][NW][BN][LD]
+    const Tile tile = resolve_tile(a);
+    if (!tile.live) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int n0 = blockIdx.x * BN;
+    const bf16* Wg = static_cast<const bf16*>(a.W) + (long long)tile.group * a.w_group_stride;
+    // loader: thread (row = tid / 2, half = tid % 2) copies four 16-byte pieces of its row per operand and k-block
+    const int lrow = tid >> 1, lhalf = (tid & 1) * 32;
+    const bf16* arow = lrow < tile.rows ? a_row<bf16>(a, tile, lrow) : nullptr;
+    const bf16* wrow[NW];
+#pragma unroll
+    for (int s = 0; s < NW; ++s) wrow[s] = n0 + lrow < a.N ? Wg + ((long long)s * a.N + n0 + lrow) * a.K : nullptr;
+    const bf16* any = static_cast<const bf16*>(a.W);
+    auto issue = [&](int kb, int stage) {
+        const int k0 = kb * BKP + lhalf;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int k = k0 + c * 8;
+            const int ab = arow && k < a.K ? 16 : 0;
+            const uint32_t adst = (uint32_t)__cvta_generic_to_shared(As + ((size_t)stage * BM + lrow) * LD + lhalf + c * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(adst), "l"(ab ? arow + k : any), "r"(ab) : "memory");
+#pragma unroll
+            for (int s = 0; s < NW; ++s) {
+                const int wb = wrow[s] && k < a.K ? 16 : 0;
+                const uint32_t wdst = (uint32_t)__cvta_generic_to_shared(Ws + (((size_t)stage * NW + s) * BN + lrow) * LD + lhalf + c * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(wdst), "l"(wb ? wrow[s] + k : any), "r"(wb) : "memory");
+            }
+        }
+    };
+    float acc[NW][2][4][4];
+#pragma unroll
+    for (int s = 0; s < NW; ++s)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[s][i][j][e] = 0.f;
+    const int k_blocks = (a.K + BKP - 1) / BKP;
+#pragma unroll
+    for (int p = 0; p < STAGES - 1; ++p) {
+        if (p < k_blocks) issue(p, p);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kb = 0; kb < k_blocks; ++kb) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();                                   // k-block kb has landed for all; the stage refilled below was used up
+        if (kb + STAGES - 1 < k_blocks) issue(kb + STAGES - 1, (kb + STAGES - 1) % STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const bf16* Ab = As + (size_t)(kb % STAGES) * BM * LD;
+        const bf16* Wb = Ws + (size_t)(kb % STAGES) * NW * BN * LD;
+#pragma unroll
+        for (int ks = 0; ks < BKP; ks += 16) {
+            uint32_t fa[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const bf16* r0 = Ab + (size_t)(wm + i * 16 + gq) * LD + ks + 2 * tq;
+                fa[i][0] = *reinterpret_cast<const uint32_t*>(r0);
+                fa[i][1] = *reinterpret_cast<const uint32_t*>(r0 + 8 * LD);
+                fa[i][2] = *reinterpret_cast<const uint32_t*>(r0 + 8);
+                fa[i][3] = *reinterpret_cast<const uint32_t*>(r0 + 8 * LD + 8);
+            }
+#pragma unroll
+            for (int s = 0; s < NW; ++s)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t fb[2];
+                    const bf16* c0 = Wb + ((size_t)s * BN + wn + j * 8 + gq) * LD + ks + 2 * tq;
+                    fb[0] = *reinterpret_cast<const uint32_t*>(c0);
+                    fb[1] = *reinterpret_cast<const uint32_t*>(c0 + 8);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) mma_bf16(acc[s][i][j], fa[i], fb);
+                }
+        }
+    }
+    bf16* C = static_cast<bf16*>(a.C) + a.c_offset + (a.tiles ? 0 : (long long)tile.group * a.c_group_stride);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = wm + i * 16 + gq + (e >> 1) * 8, n = n0 + wn + j * 8 + 2 * tq + (e & 1);
+                if (r < tile.rows && n < a.N) {
+                    float v = acc[0][i][j][e];
+                    if (GLU) v = glu(v, acc[NW - 1][i][j][e], a.limit, a.slope);
+                    C[(long long)(tile.row0 + r) * a.ldc + n] = __float2bfloat16_rn(v);
+                }
+            }
+}
+
 // ---- float32 on the CUDA cores -------------------------------------------------------------------------------
 constexpr int BK32 = 16, TM = 4, TN = 4;
 
@@ -289,7 +396,18 @@ LLM_API int llm_gemm_grouped(const void* A, long long lda, long long a_group_str
     const long long rows_y = tiles ? max_tiles : (long long)a.m_tiles * groups;
     if (rows_y > 65535) LLM_FAIL(-1, "gemm_grouped: %lld row tiles are too many for one launch", rows_y);
     dim3 grid((N + BN - 1) / BN, (unsigned)rows_y);
-    if (dtype == LLM_BF16) {
+    // few rows a group (decode steps): the streamed form; many rows: the plain tiles re-use their operands enough and run faster
+    const long long rows_about = tiles ? (long long)(max_tiles - groups) * BM : M;
+    if (dtype == LLM_BF16 && a.vec_a && a.vec_w && rows_about <= 1024) {
+        const size_t smem = (size_t)STAGES * (BM + (glu ? 2 : 1) * BN) * (BKP + PADP) * 2;
+        if (glu) {
+            cudaFuncSetAttribute(grouped_bf16_pipe_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            llm_launch(grouped_bf16_pipe_kernel<true>, grid, 128, smem, stream, a);
+        } else {
+            cudaFuncSetAttribute(grouped_bf16_pipe_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            llm_launch(grouped_bf16_pipe_kernel<false>, grid, 128, smem, stream, a);
+        }
+    } else if (dtype == LLM_BF16) {
         if (glu) llm_launch(grouped_bf16_kernel<true>, grid, 128, 0, stream, a);
         else llm_launch(grouped_bf16_kernel<false>, grid, 128, 0, stream, a);
     } else if (dtype == LLM_F32) {
