@@ -5,8 +5,8 @@
 // request times the heads of one key/value head's group (a group of more than 64 heads is cut into blocks of 64).  All rows
 // of a block share their keys and values, so a tile of 32 keys travels to shared memory once and serves every row: with one
 // latent row per token and 32 heads that is 32 times less traffic than a warp per row.  Tiles arrive by cp.async into two
-// stages, one tile ahead of the arithmetic.  Per key tile (tiles start at multiples
-// of 32 of the key position): S = Q K^T by mma.sync m16n8k16 (a warp owns 16 rows), mask and running softmax in float32
+// stages, one tile ahead of the arithmetic.  Per key tile (of 32 keys, or of 16 where two blocks with tiles of 32 would not fit an
+// SM's shared memory; tiles start at multiples of their size of the key position): S = Q K^T by mma.sync m16n8k16 (a warp owns 16 rows), mask and running softmax in float32
 // registers, P rounded to bfloat16 only as the operand of P V, V fragments by ldmatrix.trans from the row-major tile, O in
 // float32 registers.  A value head wider than 256 is cut into slices of 256 over blockIdx.z (each slice's blocks recompute
 // S).  With `splits` > 1 a block walks only its share of the key tiles and leaves (O, m, l) for the merge kernel, so a few
@@ -16,7 +16,12 @@
 
 namespace {
 
-constexpr int kRows = 64, kKeys = 32, kPad = 8;
+constexpr int kRows = 64, kPad = 8;
+
+// Keys of a tile: 32, or 16 where 32 would leave room for one block an SM only (rows of several hundred numbers).
+static inline size_t flat_smem_bytes(int key_dim, int slice_w, int shared_value, int keys) {
+    return ((size_t)(kRows + 2 * keys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * keys * (slice_w + kPad))) * 2;
+}
 
 // Width of a block's slice of the value head: wider slices recompute the scores less often but hold more of O in registers.
 static inline int slice_width(int value_dim) { return value_dim <= 64 ? 64 : value_dim <= 128 ? 128 : 256; }
@@ -44,7 +49,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NT>      // n-tiles of 8 value dims a block's slice holds (32: slices of 256, 16: of 128, 8: of 64)
+template <int NT, int kKeys>      // NT: n-tiles of 8 value dims a block's slice holds (32: slices of 256, 16: of 128, 8: of 64)
 __global__ void __launch_bounds__(128)
 attention_flat_mma_kernel(const FlatMmaArgs a) {
     pdl_trigger();
@@ -109,7 +114,8 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
     // Key (and value) tiles arrive by cp.async, one tile ahead of the arithmetic: thread (row = tid / 4, quarter = tid % 4)
     // copies every fourth 16-byte piece of its row, so it looks up one page per tile; a row that no query of the tile sees
     // is filled with zeros (copy of zero bytes).
-    const int lrow = tid >> 2, lq = tid & 3;
+    constexpr int LT = 128 / kKeys;                        // threads that share a row's copies
+    const int lrow = tid / LT, lq = tid % LT;
     auto issue = [&](int kt, int stage) {
         const int j = kt * kKeys + lrow;
         const bool live = j >= kmin && j <= kmax;
@@ -117,14 +123,14 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         const bf16* ksrc = page + (live ? key_head + (size_t)(j % a.page_size) * kd : 0);
         bf16* kdst = Ks0 + (size_t)stage * kKeys * ldk + (size_t)lrow * ldk;
         const int bytes = live ? 16 : 0;
-        for (int c = lq; c < chunks; c += 4) {
+        for (int c = lq; c < chunks; c += LT) {
             const uint32_t dst = (uint32_t)__cvta_generic_to_shared(kdst + c * 8);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(ksrc + c * 8), "r"(bytes) : "memory");
         }
         if (!a.shared_value) {
             const bf16* vsrc = page + (live ? value_plane + (size_t)(j % a.page_size) * a.value_dim + slice0 : 0);
             bf16* vdst = Vs0 + (size_t)stage * kKeys * ldv + (size_t)lrow * ldv;
-            for (int c = lq; c < vchunks; c += 4) {
+            for (int c = lq; c < vchunks; c += LT) {
                 const int vb = live && slice0 + c * 8 < a.value_dim ? 16 : 0;
                 const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vdst + c * 8);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(vb ? vsrc + c * 8 : a.cache), "r"(vb) : "memory");
@@ -147,9 +153,10 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         // S = Q K^T for the warp's 16 rows and the tile's 32 keys (a warp whose rows all lie beyond the tile's tokens, as half
         // of them do for one decoded token of 32 heads, only helps with the copies and the barriers)
         if (warp_live) {
-        float s[4][4];
+        constexpr int KB = kKeys / 8;                      // blocks of 8 keys
+        float s[KB][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < KB; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
         // fragments by ldmatrix.x4: the left operand's four 8x8 pieces of 16 rows x 16 dims at once, and the right operand's
@@ -163,7 +170,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(fa[0]), "=r"(fa[1]), "=r"(fa[2]), "=r"(fa[3]) : "r"(q_addr + ks * 2));
 #pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
+            for (int jj = 0; jj < KB / 2; ++jj) {
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(fb[0]), "=r"(fb[1]), "=r"(fb[2]), "=r"(fb[3]) : "r"(k_addr + (jj * 16 * ldk + ks) * 2));
                 mma16816(s[2 * jj], fa, fb[0], fb[1]);
@@ -176,7 +183,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         for (int e = 0; e < 2; ++e) {
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < KB; ++j)
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int key = k0 + j * 8 + 2 * tq + c;
@@ -192,7 +199,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
             corr[e] = expf(m[e] - m_use);                     // 0 while the row has seen nothing
             float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < KB; ++j)
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const float p = expf(s[j][2 * e + c] - m_use);
@@ -210,7 +217,7 @@ attention_flat_mma_kernel(const FlatMmaArgs a) {
         const bf16* vbase = a.shared_value ? Ks + slice0 : Vs;
         const int ldvv = a.shared_value ? ldk : ldv;
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
+        for (int kk = 0; kk < KB / 2; ++kk) {
             uint32_t pa[4];
             pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -296,14 +303,14 @@ LLM_API int llm_attention_flat_mma_supported(int heads, int kv_heads, int key_di
     if (key_dim % 16 || value_dim % 8 || key_dim > 1024 || value_dim > 1024 || page_stride % 8) return 0;
     if (shared_value && value_dim > key_dim) return 0;
     const int slice_w = slice_width(value_dim);
-    const size_t smem = ((size_t)(kRows + 2 * kKeys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * kKeys * (slice_w + kPad))) * 2;
-    return smem <= 200 * 1024;
+    return flat_smem_bytes(key_dim, slice_w, shared_value, 16) <= 200 * 1024;
 }
 
 // Shared memory of one block in bytes (what bounds the blocks an SM holds at wide rows).
 LLM_API int llm_attention_flat_mma_smem(int key_dim, int value_dim, int shared_value) {
     const int slice_w = slice_width(value_dim);
-    return (int)(((size_t)(kRows + 2 * kKeys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * kKeys * (slice_w + kPad))) * 2);
+    const size_t wide = flat_smem_bytes(key_dim, slice_w, shared_value, 32);
+    return (int)(2 * wide + 2048 <= 227 * 1024 ? wide : flat_smem_bytes(key_dim, slice_w, shared_value, 16));
 }
 
 // Heads of a group that one block takes (the rest of its 64 rows are neighbouring tokens).
@@ -335,19 +342,20 @@ LLM_API int llm_attention_flat_mma(const void* q, int q_stride, const void* cach
     const int group = heads / kv_heads, head_blocks = (group + a.heads_per_block - 1) / a.heads_per_block;
     const int slice_w = slice_width(value_dim);
     const int slices = (value_dim + slice_w - 1) / slice_w;
-    const size_t smem = ((size_t)(kRows + 2 * kKeys) * (key_dim + kPad) + (shared_value ? 0 : (size_t)2 * kKeys * (slice_w + kPad))) * 2;
+    // tiles of 32 keys unless two blocks of them do not fit an SM's shared memory: then tiles of 16
+    const int keys = 2 * flat_smem_bytes(key_dim, slice_w, shared_value, 32) + 2048 <= 227 * 1024 ? 32 : 16;
+    const size_t smem = flat_smem_bytes(key_dim, slice_w, shared_value, keys);
     dim3 grid((unsigned)n_tiles * splits, (unsigned)kv_heads * head_blocks, (unsigned)slices);
     if (grid.y > 65535) LLM_FAIL(-1, "attention_flat_mma: too many heads");
-    if (slice_w == 64) {
-        cudaFuncSetAttribute(attention_flat_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llm_launch(attention_flat_mma_kernel<8>, grid, 128, smem, stream, a);
-    } else if (slice_w == 128) {
-        cudaFuncSetAttribute(attention_flat_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llm_launch(attention_flat_mma_kernel<16>, grid, 128, smem, stream, a);
-    } else {
-        cudaFuncSetAttribute(attention_flat_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llm_launch(attention_flat_mma_kernel<32>, grid, 128, smem, stream, a);
-    }
+#define LLM_FLAT_MMA(NT, KEYS)                                                                                         \
+    do {                                                                                                               \
+        cudaFuncSetAttribute(attention_flat_mma_kernel<NT, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        llm_launch(attention_flat_mma_kernel<NT, KEYS>, grid, 128, smem, stream, a);                                   \
+    } while (0)
+    if (slice_w == 64) { if (keys == 32) LLM_FLAT_MMA(8, 32); else LLM_FLAT_MMA(8, 16); }
+    else if (slice_w == 128) { if (keys == 32) LLM_FLAT_MMA(16, 32); else LLM_FLAT_MMA(16, 16); }
+    else { if (keys == 32) LLM_FLAT_MMA(32, 32); else LLM_FLAT_MMA(32, 16); }
+#undef LLM_FLAT_MMA
     LLM_CHECK_LAUNCH("attention_flat_mma");
     if (splits > 1) {
         llm_launch(flat_merge_kernel, (unsigned)(tokens * heads), 128, 0, stream, (const float*)part_o, (const float*)part_ml, gate,

@@ -37,7 +37,7 @@ def rnd(*shape, dtype=torch.float32, seed=0, s=1.0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tokens,width", [(1, 8), (5, 192), (3, 2050), (2, 4099)])
+@pytest.mark.parametrize("tokens,width", [(1, 8), (5, 200), (3, 2050), (2, 4099)])
 def test_norm_add(K, dtype, tokens, width):
     res, branch, w = rnd(tokens, width, seed=1), rnd(tokens, width, dtype=dtype, seed=2, s=3.0), rnd(width, seed=3) + 1.0
     for accumulate in (True, False):
@@ -72,7 +72,7 @@ def test_linear_by_group(K, dtype, rows, groups, n, k, a_stride, lda):
     assert (out[:, :3] == 0).all()
 
 
-@pytest.mark.parametrize("outputs,top", [(16, 3), (5, 5), (100, 8), (3, 1)])
+@pytest.mark.parametrize("outputs,top", [(14, 3), (5, 5), (100, 8), (3, 1)])
 def test_route_topk(K, outputs, top):
     scores, corr = rnd(9, outputs, s=2.0), rnd(outputs, seed=6, s=0.3)
     chosen = torch.empty(9, top, dtype=torch.int32, device="cuda")
@@ -124,7 +124,7 @@ def moe_case(K, dtype, tokens, top, experts, identity, width, ff, chosen=None, s
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_routed_experts(K, dtype):
-    moe_case(K, dtype, tokens=11, top=3, experts=12, identity=4, width=40, ff=24)
+    moe_case(K, dtype, tokens=11, top=2, experts=10, identity=3, width=40, ff=24)
     moe_case(K, dtype, tokens=150, top=2, experts=3, identity=0, width=64, ff=100, seed=3)           # several tiles per expert
     moe_case(K, dtype, tokens=70, top=1, experts=5, identity=2, width=33, ff=17,
              chosen=torch.full((70, 1), 4), seed=5)                                                  # every pair on one expert
@@ -182,7 +182,7 @@ def meta_for(table, token_request, positions):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page", [(6, 2, 64, 64, 72, 16), (4, 4, 24, 40, 5, 4), (1, 1, 12, 7, 0, 8),
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page", [(4, 2, 32, 48, 40, 16), (4, 4, 24, 40, 5, 4), (1, 1, 12, 7, 0, 8),
                                                                  (8, 2, 40, 16, 33, 32), (3, 1, 130, 300, 0, 16)])
 def test_headnorm_store_and_attention(K, dtype, heads, kv_heads, dim, vdim, window, page):
     """Two requests: one stores 70 tokens in portions and is asked at every position, one stores 9."""
@@ -222,7 +222,7 @@ def test_headnorm_store_and_attention(K, dtype, heads, kv_heads, dim, vdim, wind
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dim,rot,rotary,rank,page,interleaved", [(8, 64, 32, 32, 128, 16, True), (3, 20, 12, 8, 36, 8, True),
+@pytest.mark.parametrize("heads,dim,rot,rotary,rank,page,interleaved", [(8, 48, 16, 16, 96, 16, True), (3, 20, 12, 8, 36, 8, True),
                                                                         (1, 8, 6, 6, 10, 4, False), (5, 16, 16, 0, 24, 16, True),
                                                                         (32, 32, 64, 64, 512, 16, True), (80, 16, 16, 16, 160, 32, True)])
 def test_latent_prepare_and_attention(K, dtype, heads, dim, rot, rotary, rank, page, interleaved):
@@ -263,7 +263,7 @@ def test_latent_prepare_and_attention(K, dtype, heads, dim, rot, rotary, rank, p
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dim,width,rank", [(6, 48, 192, 16), (1, 7, 20, 3), (3, 64, 96, 40), (2, 100, 64, 8), (4, 32, 50, 5)])
+@pytest.mark.parametrize("heads,dim,width,rank", [(4, 40, 160, 12), (1, 7, 20, 3), (3, 64, 96, 40), (2, 100, 64, 8), (4, 32, 50, 5)])
 def test_wkv(K, dtype, heads, dim, width, rank):
     """Three requests over four state slots; the second step continues two of them from the states the first left."""
     n = heads * dim
@@ -298,7 +298,7 @@ def test_wkv(K, dtype, heads, dim, width, rank):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window,page,total", [(16, 16, 70), (33, 8, 100), (1, 4, 9), (72, 16, 200), (0, 16, 700)])
+@pytest.mark.parametrize("window,page,total", [(16, 16, 70), (33, 8, 100), (1, 4, 9), (80, 16, 200), (0, 16, 700)])
 def test_planted_keys_at_the_window_s_edges(K, dtype, window, page, total):
     """Random weights would hide a window that is one key off: here every query points along one axis, the key just outside a
     query's window (with no window: key 3, hundreds of positions back) would take all the weight if it were seen (or, with no
